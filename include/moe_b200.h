@@ -1,0 +1,108 @@
+/* C ABI of the B200-native FP8 block-scale DeepSeek-V3 MoE shard
+ * (definition moe_fp8_block_scale_ds_routing_topk8_ng8_kg4_e32_h7168_i2048).
+ *
+ * Plain pointers and sizes only; every pointer is a DEVICE pointer unless its
+ * name says host.  All functions return 0 on success or a negative MOE_B200_E*
+ * code.  The library keeps no state between calls except a per-process cache
+ * of TMA descriptors and kernel attributes (mutex protected); all scratch
+ * memory is the caller's `workspace`.
+ */
+#ifndef MOE_B200_H_
+#define MOE_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define MOE_B200_OK 0
+#define MOE_B200_EINVAL (-1)      /* null / misaligned pointer, negative size */
+#define MOE_B200_EWORKSPACE (-2)  /* workspace smaller than moe_fp8_block_scale_workspace_bytes(T) */
+#define MOE_B200_ECUDA (-3)       /* a CUDA call failed; see moe_fp8_block_scale_last_cuda_error() */
+#define MOE_B200_EDEVICE (-4)     /* current device is not compute capability 10.x */
+#define MOE_B200_EKERNEL (-5)     /* a kernel reported an error bit (bounded wait ran out, schedule overflow) */
+
+/* Bytes of scratch the operator needs for T tokens (worst case: every token
+ * selects 8 local experts).  Includes the staging area used by ..._run_host. */
+size_t moe_fp8_block_scale_workspace_bytes(int T);
+
+/* The operator.  Replaces the reference entry point `run`
+ * (moe/solution/cuda/moe.cu:2650-2662, exported at :2898; semantics
+ * full-agent-pipeline/references/moe.py:29-40), destination-passing:
+ *   routing_logits        f32  [T, 256]
+ *   routing_bias          bf16 [256]
+ *   hidden_states         e4m3 [T, 7168]
+ *   hidden_states_scale   f32  [56, T]          (transposed, as the definition has it)
+ *   gemm1_weights         e4m3 [32, 4096, 7168]
+ *   gemm1_weights_scale   f32  [32, 32, 56]
+ *   gemm2_weights         e4m3 [32, 7168, 2048]
+ *   gemm2_weights_scale   f32  [32, 56, 16]
+ *   output                bf16 [T, 7168]        fully overwritten
+ * Asynchronous on `stream` (a cudaStream_t); never synchronises with the host,
+ * whatever T is (the reference blocks the host for T >= 512, moe.cu:2755-2759).
+ * T == 0 returns at once, like the reference (moe.cu:2664). */
+int moe_fp8_block_scale_run(const float* routing_logits, const uint16_t* routing_bias,
+                            const uint8_t* hidden_states, const float* hidden_states_scale,
+                            const uint8_t* gemm1_weights, const float* gemm1_weights_scale,
+                            const uint8_t* gemm2_weights, const float* gemm2_weights_scale,
+                            int T, int local_expert_offset, float routed_scaling_factor,
+                            uint16_t* output, void* workspace, size_t workspace_bytes, void* stream);
+
+/* Same operator for a caller whose token-side tensors live in HOST memory
+ * (pinned for full speed): copies routing_logits, routing_bias, hidden_states and
+ * hidden_states_scale to the device, runs, copies `output_host` back and waits
+ * for the stream.  Weights are layer parameters and stay device resident.
+ * The reference harness hands `run` device tensors only; this entry is what a
+ * host-side caller of that harness would otherwise write itself. */
+int moe_fp8_block_scale_run_host(const float* routing_logits_host, const uint16_t* routing_bias_host,
+                                 const uint8_t* hidden_states_host, const float* hidden_states_scale_host,
+                                 const uint8_t* gemm1_weights, const float* gemm1_weights_scale,
+                                 const uint8_t* gemm2_weights, const float* gemm2_weights_scale,
+                                 int T, int local_expert_offset, float routed_scaling_factor,
+                                 uint16_t* output_host, void* workspace, size_t workspace_bytes, void* stream);
+
+/* Waits for `stream` and returns the error bits the kernels of the last call on
+ * this workspace recorded (0 = none) in *status.  The reference checks no CUDA
+ * return code at all (moe.cu:2729-2894); this is the replacement's error channel. */
+int moe_fp8_block_scale_status(const void* workspace, void* stream, int* status);
+
+/* Last cudaError_t seen by this library on the calling thread, as an int. */
+int moe_fp8_block_scale_last_cuda_error(void);
+
+/* Where the intermediate arrays of the last call live inside the workspace
+ * (byte offsets), for parity tests that compare selection, permutation and
+ * per-stage results with the definition.  Mirrors the reference's process-global
+ * Workspace (moe.cu:2511-2589), owned by the caller instead. */
+typedef struct moe_b200_layout {
+  int32_t T, rows_cap, slab_rows, n_terms;
+  uint64_t sched;        /* moe_b200_sched                                   */
+  uint64_t topk_idx;     /* i32 [T, 8] selected global experts               */
+  uint64_t topk_w;       /* f32 [T, 8] combination weights                   */
+  uint64_t local_mask;   /* u32 [T]    bit le <=> local expert le selected   */
+  uint64_t perm_token;   /* i32 [n_sel] token of each permuted row           */
+  uint64_t perm_weight;  /* f32 [n_sel]                                      */
+  uint64_t tok_rows;     /* i32 [T, 8] rows of each token, ascending expert  */
+  uint64_t a_packed;     /* e4m3 [rows_cap, 7168] permuted activations       */
+  uint64_t g1;           /* f32 [split1][n_sel_pad, 4096] GEMM1 slabs        */
+  uint64_t cq;           /* e4m3 [n_terms][rows_cap, 2048] SwiGLU planes     */
+  uint64_t c_scale;      /* f32 [rows_cap, 16]                               */
+  uint64_t o;            /* f32 [split2][n_sel_pad, 7168] GEMM2 slabs        */
+  uint64_t total;        /* == moe_fp8_block_scale_workspace_bytes(T)        */
+} moe_b200_layout;
+
+typedef struct moe_b200_sched {
+  int32_t status, n_sel, n_sel_pad, n_active, n_tile, tiles_total, split1, split2, items1, items2;
+  int32_t pad_[6];
+  int32_t counts[32];
+  int32_t offs[33];
+  int32_t tile_prefix[33];
+} moe_b200_sched;
+
+int moe_fp8_block_scale_layout(int T, moe_b200_layout* out);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* MOE_B200_H_ */

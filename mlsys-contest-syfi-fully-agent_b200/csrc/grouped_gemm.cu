@@ -1,0 +1,313 @@
+// Grouped FP8 GEMM on tcgen05 for both expert GEMMs of the MoE shard.
+//
+// Replaces gemm_fp8_fp8_grouped_kernel / gemm_fp8_fp8_native_grouped_kernel
+// (moe/solution/cuda/moe.cu:1373-1785, GEMM1) and gemm_fp32_fp8w_fused_acc_grouped_kernel
+// (moe.cu:2186-2431, GEMM2); arithmetic contract from
+// full-agent-pipeline/references/moe.py:95-118 (block scales) and :183-196 (the two matmuls).
+//
+// Orientation ("swap-AB"): the expert's weight rows are the 128-row M operand of
+// the UMMA and the tokens are the N operand, so a batch of 1..128 tokens per
+// expert streams every weight byte through shared memory exactly once per token
+// tile and the tensor core does all fp8 decoding.  The operator is HBM-bound on
+// the weight stream in every single-GPU regime, so the kernel is organised around
+// keeping TMA loads of 16 KB weight tiles in flight:
+//
+//   warp 0  producer: TMA (SWIZZLE_128B, no multicast) of one weight tile
+//           [128 rows x 128 K-bytes] and the token tile(s) [N_TILE x 128] per K-block
+//           into a ring of STAGES shared-memory stages.
+//   warp 1  issuer: one thread issues 4 (x kNTerms for GEMM2) tcgen05.mma
+//           kind::f8f6f4 M128 x N_TILE x K32 per K-block into one of two TMEM
+//           accumulator buffers, then commits to the stage's "empty" barrier and to
+//           the buffer's "full" barrier.
+//   warps 2-5  promotion + epilogue: tcgen05.ld the K-block partial, multiply by
+//           w_scale[e, m, kb] * b_scale[row, kb] and accumulate in registers (the
+//           scales are arbitrary fp32 per 128-block, so they cannot ride on the
+//           hardware's power-of-two block scaling); after the last K-block store the
+//           fp32 tile transposed, i.e. token-major [row, m].
+//
+// Work items (expert, weight-row tile, K-split, token tile) are decoded from the
+// device-resident schedule; CTAs are persistent and take items round-robin.
+// Every mbarrier wait is bounded (ptx.cuh); on a timeout the CTA records an error
+// bit in the schedule block and leaves through the normal teardown.
+#include "kernels.h"
+#include "ptx.cuh"
+
+namespace moe {
+
+namespace {
+
+template <int GEMM, int N_TILE>
+struct Cfg {
+  static constexpr int KB = GEMM == 1 ? kKB1 : kKB2;
+  static constexpr int MT = GEMM == 1 ? kMT1 : kMT2;
+  static constexpr int M_TOTAL = MT * 128;
+  static constexpr int NTERMS = GEMM == 1 ? 1 : kNTerms;
+  static constexpr int A_BYTES = 128 * 128;
+  static constexpr int B_BYTES = N_TILE * 128;
+  static constexpr int STAGE_BYTES = A_BYTES + NTERMS * B_BYTES;
+  static constexpr int SC_BYTES = KB * N_TILE * 4;
+  static constexpr int AUX_BYTES = 1024;
+  static constexpr int BUDGET = 227 * 1024 - 1024;   // 1 KB slack for the 1024-byte alignment of the ring
+  static constexpr int STAGES_FIT = (BUDGET - SC_BYTES - AUX_BYTES) / STAGE_BYTES;
+  static constexpr int STAGES = STAGES_FIT > 10 ? 10 : STAGES_FIT;
+  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + SC_BYTES + AUX_BYTES + 1024;
+  static constexpr int TMEM_COLS = 2 * N_TILE < 32 ? 32 : 2 * N_TILE;
+  static_assert(STAGES >= 2, "ring too small");
+  static_assert((TMEM_COLS & (TMEM_COLS - 1)) == 0, "TMEM columns must be a power of two");
+};
+
+struct Aux {
+  uint64_t full[10];
+  uint64_t empty[10];
+  uint64_t tfull[2];
+  uint64_t tempty[2];
+  uint64_t esync;          // bounded replacement for a named barrier among the 128 epilogue threads
+  uint32_t tmem_base;
+  int abort;
+  int prefix[kELocal + 1];
+  int offs[kELocal + 1];
+};
+static_assert(sizeof(Aux) <= 1024, "Aux must fit its slot");
+
+struct Item {
+  int e, m, s, row0, valid, kb0, kb1;
+};
+
+template <int GEMM, int N_TILE>
+__device__ __forceinline__ Item decode_item(int i, int split, const Aux* aux) {
+  using C = Cfg<GEMM, N_TILE>;
+  const int per = C::MT * split;
+  int e = 0;
+#pragma unroll 1
+  for (int k = 16; k > 0; k >>= 1)
+    if (e + k < kELocal && aux->prefix[e + k] * per <= i) e += k;
+  // skip experts without tiles that share the same prefix value
+  while (e < kELocal - 1 && aux->prefix[e + 1] * per <= i) ++e;
+  int r = i - aux->prefix[e] * per;
+  const int tiles_e = aux->prefix[e + 1] - aux->prefix[e];
+  const int n = r % tiles_e;
+  r /= tiles_e;
+  Item it;
+  it.e = e;
+  it.s = r % split;
+  it.m = r / split;
+  const int cnt = aux->offs[e + 1] - aux->offs[e];
+  it.row0 = aux->offs[e] + n * N_TILE;
+  it.valid = min(N_TILE, cnt - n * N_TILE);
+  it.kb0 = (it.s * C::KB) / split;
+  it.kb1 = ((it.s + 1) * C::KB) / split;
+  return it;
+}
+
+template <int GEMM, int N_TILE>
+__global__ void __launch_bounds__(192, 1)
+grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_b, GemmArgs a) {
+  using C = Cfg<GEMM, N_TILE>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  float* sc = reinterpret_cast<float*>(smem + C::STAGES * C::STAGE_BYTES);
+  Aux* aux = reinterpret_cast<Aux*>(smem + C::STAGES * C::STAGE_BYTES + C::SC_BYTES);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  MoeSched* sched = a.sched;
+  const int items = GEMM == 1 ? sched->items1 : sched->items2;
+  const int split = GEMM == 1 ? sched->split1 : sched->split2;
+  const int n_sel_pad = sched->n_sel_pad;
+
+  if (threadIdx.x <= kELocal) {
+    aux->prefix[threadIdx.x] = sched->tile_prefix[threadIdx.x];
+    aux->offs[threadIdx.x] = sched->offs[threadIdx.x];
+  }
+  if (threadIdx.x == 0) {
+    aux->abort = 0;
+    for (int s = 0; s < C::STAGES; ++s) {
+      mbar_init(smem_u32(&aux->full[s]), 1);
+      mbar_init(smem_u32(&aux->empty[s]), 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(smem_u32(&aux->tfull[b]), 1);
+      mbar_init(smem_u32(&aux->tempty[b]), 4);
+    }
+    mbar_init(smem_u32(&aux->esync), 128);
+    fence_mbar_init();
+    tma_prefetch_desc(&tm_w);
+    tma_prefetch_desc(&tm_b);
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(&aux->tmem_base), C::TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = aux->tmem_base;
+  volatile int* abort_flag = &aux->abort;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      uint32_t it = 0;
+      bool ok = true;
+      for (int i = blockIdx.x; ok && i < items; i += gridDim.x) {
+        const Item w = decode_item<GEMM, N_TILE>(i, split, aux);
+        const int wy = w.e * C::M_TOTAL + w.m * 128;
+        for (int kb = w.kb0; kb < w.kb1; ++kb, ++it) {
+          const uint32_t stage = it % C::STAGES, ph = (it / C::STAGES) & 1u;
+          if (!mbar_wait(smem_u32(&aux->empty[stage]), ph ^ 1u, abort_flag)) { ok = false; break; }
+          const uint32_t bar = smem_u32(&aux->full[stage]);
+          mbar_arrive_expect_tx(bar, C::STAGE_BYTES);
+          const uint32_t dst = smem_u32(smem + stage * C::STAGE_BYTES);
+          tma_load_2d(dst, &tm_w, kb * 128, wy, bar);
+#pragma unroll
+          for (int t = 0; t < C::NTERMS; ++t)
+            tma_load_2d(dst + C::A_BYTES + t * C::B_BYTES, &tm_b, kb * 128, t * a.b_plane_rows + w.row0, bar);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ UMMA issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc = umma_idesc_e4m3(128, N_TILE);
+      uint32_t it = 0;
+      bool ok = true;
+      for (int i = blockIdx.x; ok && i < items; i += gridDim.x) {
+        const Item w = decode_item<GEMM, N_TILE>(i, split, aux);
+        for (int kb = w.kb0; kb < w.kb1; ++kb, ++it) {
+          const uint32_t stage = it % C::STAGES, ph = (it / C::STAGES) & 1u;
+          const uint32_t buf = it & 1u, bph = (it >> 1) & 1u;
+          if (!mbar_wait(smem_u32(&aux->tempty[buf]), bph ^ 1u, abort_flag)) { ok = false; break; }
+          if (!mbar_wait(smem_u32(&aux->full[stage]), ph, abort_flag)) { ok = false; break; }
+          tc_fence_after_sync();
+          const uint32_t sa = smem_u32(smem + stage * C::STAGE_BYTES);
+          const uint64_t adesc = umma_desc_k_sw128(sa);
+          const uint32_t d = tmem_base + buf * N_TILE;
+#pragma unroll
+          for (int t = 0; t < C::NTERMS; ++t) {
+            const uint64_t bdesc = umma_desc_k_sw128(sa + C::A_BYTES + t * C::B_BYTES);
+#pragma unroll
+            for (int k4 = 0; k4 < 4; ++k4)   // +32 bytes of K inside the 128-byte swizzle atom = +2 encoded units
+              umma_f8(d, adesc + 2 * k4, bdesc + 2 * k4, idesc, (t | k4) != 0 ? 1u : 0u);
+          }
+          umma_commit(smem_u32(&aux->empty[stage]));
+          umma_commit(smem_u32(&aux->tfull[buf]));
+        }
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ promotion + epilogue (warps 2..5)
+    const int q = warp & 3;                       // TMEM lane quarter this warp may access
+    const int etid = threadIdx.x - 64;            // 0..127
+    const uint32_t lane_addr = static_cast<uint32_t>(q * 32) << 16;
+    uint32_t it = 0, eph = 0;
+    bool ok = true;
+    // all 128 epilogue threads meet here; bounded like every other wait in this kernel
+    auto epi_sync = [&]() {
+      mbar_arrive(smem_u32(&aux->esync));
+      if (!mbar_wait(smem_u32(&aux->esync), eph, abort_flag)) ok = false;
+      eph ^= 1u;
+    };
+    for (int i = blockIdx.x; ok && i < items; i += gridDim.x) {
+      const Item w = decode_item<GEMM, N_TILE>(i, split, aux);
+      const int nkb = w.kb1 - w.kb0;
+      epi_sync();   // the previous item's scale products are no longer being read
+      if (!ok) break;
+      const float* ws = a.w_scale + (static_cast<size_t>(w.e) * C::MT + w.m) * C::KB;
+      for (int idx = etid; idx < nkb * N_TILE; idx += 128) {
+        const int kbl = idx / N_TILE, j = idx % N_TILE, kb = w.kb0 + kbl;
+        float bs = 0.0f;
+        if (j < w.valid) {
+          if (GEMM == 1) bs = __ldg(a.b_scale + static_cast<size_t>(kb) * a.T + __ldg(a.perm_token + w.row0 + j));
+          else bs = __ldg(a.b_scale + static_cast<size_t>(w.row0 + j) * kKB2 + kb);
+        }
+        sc[idx] = __ldg(ws + kb) * bs;
+      }
+      epi_sync();
+      if (!ok) break;
+
+      float acc[N_TILE];
+#pragma unroll
+      for (int j = 0; j < N_TILE; ++j) acc[j] = 0.0f;
+
+      for (int kbl = 0; kbl < nkb; ++kbl, ++it) {
+        const uint32_t buf = it & 1u, bph = (it >> 1) & 1u;
+        if (!mbar_wait(smem_u32(&aux->tfull[buf]), bph, abort_flag)) { ok = false; break; }
+        tc_fence_after_sync();
+        const uint32_t taddr = tmem_base + lane_addr + buf * N_TILE;
+        const float4* scv = reinterpret_cast<const float4*>(sc + kbl * N_TILE);
+#pragma unroll
+        for (int c = 0; c < N_TILE / 16; ++c) {
+          float v[16];
+          tmem_ld16(taddr + c * 16, v);
+          tmem_wait_ld();
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            const float4 f = scv[c * 4 + u];
+            acc[c * 16 + u * 4 + 0] = fmaf(v[u * 4 + 0], f.x, acc[c * 16 + u * 4 + 0]);
+            acc[c * 16 + u * 4 + 1] = fmaf(v[u * 4 + 1], f.y, acc[c * 16 + u * 4 + 1]);
+            acc[c * 16 + u * 4 + 2] = fmaf(v[u * 4 + 2], f.z, acc[c * 16 + u * 4 + 2]);
+            acc[c * 16 + u * 4 + 3] = fmaf(v[u * 4 + 3], f.w, acc[c * 16 + u * 4 + 3]);
+          }
+        }
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(smem_u32(&aux->tempty[buf]));
+      }
+      if (!ok) break;
+      float* out = a.out + (static_cast<size_t>(w.s) * n_sel_pad + w.row0) * C::M_TOTAL + w.m * 128 + q * 32 + lane;
+#pragma unroll
+      for (int j = 0; j < N_TILE; ++j)
+        if (j < w.valid) out[static_cast<size_t>(j) * C::M_TOTAL] = acc[j];
+    }
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (threadIdx.x == 0 && aux->abort) atomicOr(&sched->status, GEMM == 1 ? kErrGemm1Timeout : kErrGemm2Timeout);
+  if (warp == 1) {
+    __syncwarp();
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, C::TMEM_COLS);
+  }
+}
+
+template <int GEMM, int N_TILE>
+int launch_one(const CUtensorMap& tm_w, const CUtensorMap& tm_b, const GemmArgs& a, int ctas, cudaStream_t stream) {
+  using C = Cfg<GEMM, N_TILE>;
+  grouped_gemm_kernel<GEMM, N_TILE><<<ctas, 192, C::SMEM_BYTES, stream>>>(tm_w, tm_b, a);
+  return static_cast<int>(cudaGetLastError());
+}
+
+template <int GEMM, int N_TILE>
+int init_one() {
+  using C = Cfg<GEMM, N_TILE>;
+  return static_cast<int>(cudaFuncSetAttribute(grouped_gemm_kernel<GEMM, N_TILE>,
+                                               cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES));
+}
+
+}  // namespace
+
+int grouped_gemm_init() {
+  int rc = 0;
+  if ((rc = init_one<1, 16>())) return rc;
+  if ((rc = init_one<1, 32>())) return rc;
+  if ((rc = init_one<1, 64>())) return rc;
+  if ((rc = init_one<1, 128>())) return rc;
+  if ((rc = init_one<2, 16>())) return rc;
+  if ((rc = init_one<2, 32>())) return rc;
+  if ((rc = init_one<2, 64>())) return rc;
+  if ((rc = init_one<2, 128>())) return rc;
+  return 0;
+}
+
+int launch_grouped_gemm(int gemm_id, int n_tile, const CUtensorMap& tm_w, const CUtensorMap& tm_b, const GemmArgs& a,
+                        int ctas, cudaStream_t stream) {
+#define MOE_CASE(G, N) \
+  if (gemm_id == G && n_tile == N) return launch_one<G, N>(tm_w, tm_b, a, ctas, stream);
+  MOE_CASE(1, 16) MOE_CASE(1, 32) MOE_CASE(1, 64) MOE_CASE(1, 128)
+  MOE_CASE(2, 16) MOE_CASE(2, 32) MOE_CASE(2, 64) MOE_CASE(2, 128)
+#undef MOE_CASE
+  return static_cast<int>(cudaErrorInvalidValue);
+}
+
+}  // namespace moe

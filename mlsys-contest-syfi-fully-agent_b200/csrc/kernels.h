@@ -1,0 +1,84 @@
+// Argument blocks and host-side launch functions of the kernels.
+#pragma once
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "moe_layout.h"
+
+namespace moe {
+
+struct RouteArgs {
+  const float* logits;          // [T, 256]
+  const uint16_t* bias_bf16;    // [256]
+  int T;
+  int local_expert_offset;
+  float routed_scaling_factor;
+  int* topk_idx;                // [T, 8] global expert ids, descending biased score
+  float* topk_w;                // [T, 8] combination weights
+  uint32_t* local_mask;         // [T] bit le set when local expert le is selected
+};
+
+struct PermuteArgs {
+  int T;
+  int local_expert_offset;
+  int n_tile;                   // token-tile width the GEMMs will use
+  int ctas;                     // persistent CTAs the GEMMs will run
+  int rows_cap, slab_rows;
+  const uint32_t* local_mask;
+  const int* topk_idx;
+  const float* topk_w;
+  MoeSched* sched;
+  int* perm_token;              // [n_sel] token of each row
+  float* perm_weight;           // [n_sel] combination weight of each row
+  int* tok_rows;                // [T, 8] rows of a token in ascending local expert order
+};
+
+struct GatherArgs {
+  const MoeSched* sched;
+  const int* perm_token;
+  const uint8_t* hidden;        // [T, 7168] e4m3
+  uint8_t* a_packed;            // [rows_cap, 7168]
+};
+
+// Grouped, swap-AB, split-K fp8 GEMM: out[slab][row, m] = sum_k W_e[m, k] * B[row, k] with the
+// 128-block scales applied per K-block.  Used for GEMM1 (B = packed activations) and
+// GEMM2 (B = kNTerms e4m3 planes of the SwiGLU output).
+struct GemmArgs {
+  MoeSched* sched;
+  const float* w_scale;         // [32, M/128, K/128]
+  const float* b_scale;         // GEMM1: hidden_states_scale [56, T]; GEMM2: c_scale [rows, 16]
+  const int* perm_token;        // GEMM1: token of each row (to index b_scale); GEMM2: unused
+  int T;
+  int b_plane_rows;             // GEMM2: rows between consecutive e4m3 planes of B (rows_cap); GEMM1: 0
+  float* out;                   // fp32 slabs [split][n_sel_pad, M]
+};
+
+struct SwigluArgs {
+  const MoeSched* sched;
+  const float* g1;              // slabs [split1][n_sel_pad, 4096]
+  uint8_t* cq;                  // [kNTerms][rows_cap, 2048] e4m3 planes
+  float* c_scale;               // [rows_cap, 16] power-of-two plane scale per 128 block
+  int rows_cap;
+};
+
+struct CombineArgs {
+  const MoeSched* sched;
+  const float* o;               // slabs [split2][n_sel_pad, 7168]
+  const uint32_t* local_mask;
+  const int* tok_rows;
+  const float* perm_weight;
+  uint16_t* out_bf16;           // [T, 7168]
+  int T;
+};
+
+void launch_route_permute(const RouteArgs& r, const PermuteArgs& p, cudaStream_t stream);
+void launch_gather_rows(const GatherArgs& a, int T, cudaStream_t stream);
+// gemm_id 1 or 2; n_tile in {16, 32, 64, 128}.  Returns a cudaError_t as int.
+int launch_grouped_gemm(int gemm_id, int n_tile, const CUtensorMap& tm_w, const CUtensorMap& tm_b, const GemmArgs& a,
+                        int ctas, cudaStream_t stream);
+int grouped_gemm_init();   // one-time function attributes (dynamic shared memory opt-in)
+void launch_swiglu_split(const SwigluArgs& a, int T, cudaStream_t stream);
+void launch_combine(const CombineArgs& a, cudaStream_t stream);
+
+}  // namespace moe

@@ -1,0 +1,297 @@
+// Host launcher and C ABI (declared in include/moe_b200.h).
+//
+// Replaces run_impl and the process-global Workspace of the reference solution
+// (moe/solution/cuda/moe.cu:2511-2589, 2650-2896).  One code path for every token
+// count: route+permute -> gather -> GEMM1 -> SwiGLU/split -> GEMM2 -> combine,
+// all asynchronous on the caller's stream, scratch memory owned by the caller.
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include <cstdlib>
+#include <cstring>
+#include <mutex>
+
+#include "../../include/moe_b200.h"
+#include "kernels.h"
+
+namespace moe {
+namespace {
+
+thread_local int g_last_cuda_error = 0;
+
+#define MOE_CUDA(expr)                                   \
+  do {                                                   \
+    cudaError_t e__ = (expr);                            \
+    if (e__ != cudaSuccess) {                            \
+      g_last_cuda_error = static_cast<int>(e__);         \
+      return MOE_B200_ECUDA;                             \
+    }                                                    \
+  } while (0)
+
+// Staging area for ..._run_host, appended to the kernel workspace.
+struct HostStage {
+  size_t logits, bias, hidden, hscale, out, total;
+};
+HostStage make_stage(int T, size_t base) {
+  HostStage s{};
+  size_t off = base;
+  auto take = [&](size_t b) { size_t o = off; off = align_up(off + b, 256); return o; };
+  const size_t Tz = T > 0 ? T : 1;
+  s.logits = take(Tz * kEGlobal * 4);
+  s.bias = take(kEGlobal * 2);
+  s.hidden = take(Tz * kH);
+  s.hscale = take(Tz * kKB1 * 4);
+  s.out = take(Tz * kH * 2);
+  s.total = off;
+  return s;
+}
+
+using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                              const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                              CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+struct DeviceState {
+  bool ready = false;
+  int sm_count = 0;
+  int cc_major = 0;
+  EncodeFn encode = nullptr;
+};
+std::mutex g_mu;
+DeviceState g_dev[16];
+
+struct MapKey {
+  const void* ptr;
+  uint64_t rows, cols;
+  uint32_t box_rows;
+};
+struct MapEntry {
+  MapKey key;
+  CUtensorMap map;
+  bool used;
+};
+MapEntry g_maps[32];
+int g_map_next = 0;
+
+int ensure_device(DeviceState** out) {
+  int dev = 0;
+  MOE_CUDA(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 16) return MOE_B200_EINVAL;
+  std::lock_guard<std::mutex> lk(g_mu);
+  DeviceState& d = g_dev[dev];
+  if (!d.ready) {
+    MOE_CUDA(cudaDeviceGetAttribute(&d.cc_major, cudaDevAttrComputeCapabilityMajor, dev));
+    MOE_CUDA(cudaDeviceGetAttribute(&d.sm_count, cudaDevAttrMultiProcessorCount, dev));
+    if (d.cc_major != 10) return MOE_B200_EDEVICE;
+    void* fn = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    MOE_CUDA(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres));
+    if (fn == nullptr || qres != cudaDriverEntryPointSuccess) return MOE_B200_EDEVICE;
+    d.encode = reinterpret_cast<EncodeFn>(fn);
+    int rc = grouped_gemm_init();
+    if (rc != 0) {
+      g_last_cuda_error = rc;
+      return MOE_B200_ECUDA;
+    }
+    d.ready = true;
+  }
+  *out = &d;
+  return MOE_B200_OK;
+}
+
+// 2-D u8 tensor [rows, cols] row-major, box [box_rows, 128 bytes], 128-byte swizzle.
+int get_map(DeviceState* d, const void* ptr, uint64_t rows, uint64_t cols, uint32_t box_rows, CUtensorMap* out) {
+  std::lock_guard<std::mutex> lk(g_mu);
+  for (auto& e : g_maps)
+    if (e.used && e.key.ptr == ptr && e.key.rows == rows && e.key.cols == cols && e.key.box_rows == box_rows) {
+      *out = e.map;
+      return MOE_B200_OK;
+    }
+  cuuint64_t dims[2] = {cols, rows};
+  cuuint64_t strides[1] = {cols};
+  cuuint32_t box[2] = {128, box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUtensorMap m;
+  CUresult r = d->encode(&m, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(ptr), dims, strides, box, estr,
+                         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    g_last_cuda_error = 100000 + static_cast<int>(r);
+    return MOE_B200_ECUDA;
+  }
+  MapEntry& e = g_maps[g_map_next];
+  g_map_next = (g_map_next + 1) % 32;
+  e.key = MapKey{ptr, rows, cols, box_rows};
+  e.map = m;
+  e.used = true;
+  *out = m;
+  return MOE_B200_OK;
+}
+
+int pick_n_tile(int T) {
+  static const int forced = [] {
+    const char* s = std::getenv("MOE_B200_NTILE");
+    return s ? std::atoi(s) : 0;
+  }();
+  if (forced == 16 || forced == 32 || forced == 64 || forced == 128) return forced;
+  return T <= 16 ? 16 : T <= 32 ? 32 : T <= 64 ? 64 : 128;
+}
+
+bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+}  // namespace
+}  // namespace moe
+
+using namespace moe;
+
+extern "C" size_t moe_fp8_block_scale_workspace_bytes(int T) {
+  if (T < 0) return 0;
+  const WorkspaceLayout L = make_layout(T);
+  return make_stage(T, L.total).total;
+}
+
+extern "C" int moe_fp8_block_scale_last_cuda_error(void) { return g_last_cuda_error; }
+
+extern "C" int moe_fp8_block_scale_layout(int T, moe_b200_layout* out) {
+  if (T < 0 || out == nullptr) return MOE_B200_EINVAL;
+  static_assert(sizeof(moe_b200_sched) == sizeof(MoeSched), "public and internal schedule structs differ");
+  const WorkspaceLayout L = make_layout(T);
+  out->T = T;
+  out->rows_cap = L.rows_cap;
+  out->slab_rows = L.slab_rows;
+  out->n_terms = kNTerms;
+  out->sched = L.sched;
+  out->topk_idx = L.topk_idx;
+  out->topk_w = L.topk_w;
+  out->local_mask = L.local_mask;
+  out->perm_token = L.perm_token;
+  out->perm_weight = L.perm_weight;
+  out->tok_rows = L.tok_rows;
+  out->a_packed = L.a_packed;
+  out->g1 = L.g1;
+  out->cq = L.cq;
+  out->c_scale = L.c_scale;
+  out->o = L.o;
+  out->total = moe_fp8_block_scale_workspace_bytes(T);
+  return MOE_B200_OK;
+}
+
+extern "C" int moe_fp8_block_scale_run(const float* routing_logits, const uint16_t* routing_bias,
+                                       const uint8_t* hidden_states, const float* hidden_states_scale,
+                                       const uint8_t* gemm1_weights, const float* gemm1_weights_scale,
+                                       const uint8_t* gemm2_weights, const float* gemm2_weights_scale, int T,
+                                       int local_expert_offset, float routed_scaling_factor, uint16_t* output,
+                                       void* workspace, size_t workspace_bytes, void* stream_v) {
+  if (T < 0) return MOE_B200_EINVAL;
+  if (T == 0) return MOE_B200_OK;
+  if (!routing_logits || !routing_bias || !hidden_states || !hidden_states_scale || !gemm1_weights ||
+      !gemm1_weights_scale || !gemm2_weights || !gemm2_weights_scale || !output || !workspace)
+    return MOE_B200_EINVAL;
+  if (!aligned16(hidden_states) || !aligned16(gemm1_weights) || !aligned16(gemm2_weights) || !aligned16(output) ||
+      (reinterpret_cast<uintptr_t>(workspace) & 1023u) != 0)
+    return MOE_B200_EINVAL;
+  if (workspace_bytes < moe_fp8_block_scale_workspace_bytes(T)) return MOE_B200_EWORKSPACE;
+  DeviceState* dev = nullptr;
+  int rc = ensure_device(&dev);
+  if (rc != MOE_B200_OK) return rc;
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
+
+  const WorkspaceLayout L = make_layout(T);
+  uint8_t* ws = static_cast<uint8_t*>(workspace);
+  MoeSched* sched = reinterpret_cast<MoeSched*>(ws + L.sched);
+  int* topk_idx = reinterpret_cast<int*>(ws + L.topk_idx);
+  float* topk_w = reinterpret_cast<float*>(ws + L.topk_w);
+  uint32_t* local_mask = reinterpret_cast<uint32_t*>(ws + L.local_mask);
+  int* perm_token = reinterpret_cast<int*>(ws + L.perm_token);
+  float* perm_weight = reinterpret_cast<float*>(ws + L.perm_weight);
+  int* tok_rows = reinterpret_cast<int*>(ws + L.tok_rows);
+  uint8_t* a_packed = ws + L.a_packed;
+  float* g1 = reinterpret_cast<float*>(ws + L.g1);
+  uint8_t* cq = ws + L.cq;
+  float* c_scale = reinterpret_cast<float*>(ws + L.c_scale);
+  float* o = reinterpret_cast<float*>(ws + L.o);
+
+  const int n_tile = pick_n_tile(T);
+  const int ctas = dev->sm_count;
+
+  CUtensorMap tm_w13, tm_w2, tm_a, tm_c;
+  if ((rc = get_map(dev, gemm1_weights, static_cast<uint64_t>(kELocal) * k2I, kH, 128, &tm_w13))) return rc;
+  if ((rc = get_map(dev, gemm2_weights, static_cast<uint64_t>(kELocal) * kH, kI, 128, &tm_w2))) return rc;
+  if ((rc = get_map(dev, a_packed, L.rows_cap, kH, n_tile, &tm_a))) return rc;
+  if ((rc = get_map(dev, cq, static_cast<uint64_t>(kNTerms) * L.rows_cap, kI, n_tile, &tm_c))) return rc;
+
+  RouteArgs ra{routing_logits, routing_bias, T, local_expert_offset, routed_scaling_factor, topk_idx, topk_w,
+               local_mask};
+  PermuteArgs pa{T, local_expert_offset, n_tile, ctas, L.rows_cap, L.slab_rows, local_mask, topk_idx, topk_w,
+                 sched, perm_token, perm_weight, tok_rows};
+  launch_route_permute(ra, pa, stream);
+  MOE_CUDA(cudaGetLastError());
+
+  GatherArgs ga{sched, perm_token, hidden_states, a_packed};
+  launch_gather_rows(ga, T, stream);
+  MOE_CUDA(cudaGetLastError());
+
+  GemmArgs g1a{sched, gemm1_weights_scale, hidden_states_scale, perm_token, T, 0, g1};
+  if ((rc = launch_grouped_gemm(1, n_tile, tm_w13, tm_a, g1a, ctas, stream))) {
+    g_last_cuda_error = rc;
+    return MOE_B200_ECUDA;
+  }
+
+  SwigluArgs sa{sched, g1, cq, c_scale, L.rows_cap};
+  launch_swiglu_split(sa, T, stream);
+  MOE_CUDA(cudaGetLastError());
+
+  GemmArgs g2a{sched, gemm2_weights_scale, c_scale, nullptr, T, L.rows_cap, o};
+  if ((rc = launch_grouped_gemm(2, n_tile, tm_w2, tm_c, g2a, ctas, stream))) {
+    g_last_cuda_error = rc;
+    return MOE_B200_ECUDA;
+  }
+
+  CombineArgs ca{sched, o, local_mask, tok_rows, perm_weight, output, T};
+  launch_combine(ca, stream);
+  MOE_CUDA(cudaGetLastError());
+  return MOE_B200_OK;
+}
+
+extern "C" int moe_fp8_block_scale_run_host(const float* routing_logits_host, const uint16_t* routing_bias_host,
+                                            const uint8_t* hidden_states_host, const float* hidden_states_scale_host,
+                                            const uint8_t* gemm1_weights, const float* gemm1_weights_scale,
+                                            const uint8_t* gemm2_weights, const float* gemm2_weights_scale, int T,
+                                            int local_expert_offset, float routed_scaling_factor,
+                                            uint16_t* output_host, void* workspace, size_t workspace_bytes,
+                                            void* stream_v) {
+  if (T < 0) return MOE_B200_EINVAL;
+  if (T == 0) return MOE_B200_OK;
+  if (!routing_logits_host || !routing_bias_host || !hidden_states_host || !hidden_states_scale_host || !output_host ||
+      !workspace)
+    return MOE_B200_EINVAL;
+  if (workspace_bytes < moe_fp8_block_scale_workspace_bytes(T)) return MOE_B200_EWORKSPACE;
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
+  const HostStage st = make_stage(T, make_layout(T).total);
+  uint8_t* ws = static_cast<uint8_t*>(workspace);
+  float* d_logits = reinterpret_cast<float*>(ws + st.logits);
+  uint16_t* d_bias = reinterpret_cast<uint16_t*>(ws + st.bias);
+  uint8_t* d_hidden = ws + st.hidden;
+  float* d_hscale = reinterpret_cast<float*>(ws + st.hscale);
+  uint16_t* d_out = reinterpret_cast<uint16_t*>(ws + st.out);
+  const size_t Tz = static_cast<size_t>(T);
+  MOE_CUDA(cudaMemcpyAsync(d_logits, routing_logits_host, Tz * kEGlobal * 4, cudaMemcpyHostToDevice, stream));
+  MOE_CUDA(cudaMemcpyAsync(d_bias, routing_bias_host, kEGlobal * 2, cudaMemcpyHostToDevice, stream));
+  MOE_CUDA(cudaMemcpyAsync(d_hidden, hidden_states_host, Tz * kH, cudaMemcpyHostToDevice, stream));
+  MOE_CUDA(cudaMemcpyAsync(d_hscale, hidden_states_scale_host, Tz * kKB1 * 4, cudaMemcpyHostToDevice, stream));
+  int rc = moe_fp8_block_scale_run(d_logits, d_bias, d_hidden, d_hscale, gemm1_weights, gemm1_weights_scale,
+                                   gemm2_weights, gemm2_weights_scale, T, local_expert_offset, routed_scaling_factor,
+                                   d_out, workspace, workspace_bytes, stream_v);
+  if (rc != MOE_B200_OK) return rc;
+  MOE_CUDA(cudaMemcpyAsync(output_host, d_out, Tz * kH * 2, cudaMemcpyDeviceToHost, stream));
+  MOE_CUDA(cudaStreamSynchronize(stream));
+  return MOE_B200_OK;
+}
+
+extern "C" int moe_fp8_block_scale_status(const void* workspace, void* stream_v, int* status) {
+  if (!workspace || !status) return MOE_B200_EINVAL;
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
+  MOE_CUDA(cudaStreamSynchronize(stream));
+  const WorkspaceLayout L = make_layout(1);
+  MOE_CUDA(cudaMemcpy(status, static_cast<const uint8_t*>(workspace) + L.sched, sizeof(int), cudaMemcpyDeviceToHost));
+  return *status == 0 ? MOE_B200_OK : MOE_B200_EKERNEL;
+}

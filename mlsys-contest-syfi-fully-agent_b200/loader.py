@@ -1,0 +1,90 @@
+"""ctypes binding of the C-ABI library (include/moe_b200.h).
+
+There is no fallback: if ``libmoe_b200.so`` has not been built
+(``python -m`` of ``build.py`` or ``__graft_entry__.build()``), importing
+this module raises.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(HERE, "libmoe_b200.so")
+
+OK, EINVAL, EWORKSPACE, ECUDA, EDEVICE, EKERNEL = 0, -1, -2, -3, -4, -5
+ERROR_NAMES = {OK: "ok", EINVAL: "invalid argument", EWORKSPACE: "workspace too small", ECUDA: "CUDA error",
+               EDEVICE: "device is not sm_100", EKERNEL: "kernel reported an error"}
+
+EXPORTS = [
+    "moe_fp8_block_scale_workspace_bytes",
+    "moe_fp8_block_scale_run",
+    "moe_fp8_block_scale_run_host",
+    "moe_fp8_block_scale_status",
+    "moe_fp8_block_scale_last_cuda_error",
+    "moe_fp8_block_scale_layout",
+]
+
+
+class Layout(ctypes.Structure):
+    _fields_ = [("T", ctypes.c_int32), ("rows_cap", ctypes.c_int32), ("slab_rows", ctypes.c_int32),
+                ("n_terms", ctypes.c_int32)] + \
+               [(n, ctypes.c_uint64) for n in ("sched", "topk_idx", "topk_w", "local_mask", "perm_token",
+                                               "perm_weight", "tok_rows", "a_packed", "g1", "cq", "c_scale", "o",
+                                               "total")]
+
+
+class Sched(ctypes.Structure):
+    _fields_ = [(n, ctypes.c_int32) for n in ("status", "n_sel", "n_sel_pad", "n_active", "n_tile", "tiles_total",
+                                              "split1", "split2", "items1", "items2")] + \
+               [("pad_", ctypes.c_int32 * 6), ("counts", ctypes.c_int32 * 32), ("offs", ctypes.c_int32 * 33),
+                ("tile_prefix", ctypes.c_int32 * 33)]
+
+
+class MoeLibraryError(RuntimeError):
+    def __init__(self, code: int, cuda_error: int = 0):
+        self.code, self.cuda_error = code, cuda_error
+        msg = ERROR_NAMES.get(code, f"error {code}")
+        if code == ECUDA:
+            msg += f" (cudaError {cuda_error})"
+        super().__init__(msg)
+
+
+def _load() -> ctypes.CDLL:
+    if not os.path.exists(LIB_PATH):
+        raise ImportError(f"{LIB_PATH} is missing: build it first (python __graft_entry__.py build); "
+                          "there is no non-CUDA fallback")
+    lib = ctypes.CDLL(LIB_PATH)
+    vp, i32, f32, sz = ctypes.c_void_p, ctypes.c_int, ctypes.c_float, ctypes.c_size_t
+    lib.moe_fp8_block_scale_workspace_bytes.restype = sz
+    lib.moe_fp8_block_scale_workspace_bytes.argtypes = [i32]
+    run_args = [vp] * 8 + [i32, i32, f32, vp, vp, sz, vp]
+    lib.moe_fp8_block_scale_run.restype = i32
+    lib.moe_fp8_block_scale_run.argtypes = run_args
+    lib.moe_fp8_block_scale_run_host.restype = i32
+    lib.moe_fp8_block_scale_run_host.argtypes = run_args
+    lib.moe_fp8_block_scale_status.restype = i32
+    lib.moe_fp8_block_scale_status.argtypes = [vp, vp, ctypes.POINTER(i32)]
+    lib.moe_fp8_block_scale_last_cuda_error.restype = i32
+    lib.moe_fp8_block_scale_last_cuda_error.argtypes = []
+    lib.moe_fp8_block_scale_layout.restype = i32
+    lib.moe_fp8_block_scale_layout.argtypes = [i32, ctypes.POINTER(Layout)]
+    return lib
+
+
+lib = _load()
+
+
+def check(code: int):
+    if code != OK:
+        raise MoeLibraryError(code, lib.moe_fp8_block_scale_last_cuda_error())
+
+
+def workspace_bytes(T: int) -> int:
+    return int(lib.moe_fp8_block_scale_workspace_bytes(int(T)))
+
+
+def layout(T: int) -> Layout:
+    out = Layout()
+    check(lib.moe_fp8_block_scale_layout(int(T), ctypes.byref(out)))
+    return out

@@ -1,0 +1,192 @@
+"""Host-side mirror of the reference operator interface.
+
+``run`` takes the eleven arguments of the reference solution's entry point in
+the same order and with the same meaning (moe/solution/cuda/moe.cu:2650-2662;
+definition full-agent-pipeline/references/moe.py:29-40), destination passing:
+the last argument is the pre-allocated bf16 output.  It validates shapes and
+dtypes the way the definition asserts them (references/moe.py:66-87) and calls
+the C ABI (include/moe_b200.h) on torch's current CUDA stream.  torch is only
+used for device memory and streams.
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import Dict, Optional
+
+import torch
+
+from . import loader
+
+H, I, E_LOCAL, E_GLOBAL, BLOCK = 7168, 2048, 32, 256, 128
+
+
+class Workspace:
+    """Caller-owned scratch memory, grown on demand (the counterpart of the
+    reference's process-global ``Workspace``, moe.cu:2511-2589, but per object
+    and released with it)."""
+
+    def __init__(self, device=None):
+        self.device = torch.device(device if device is not None else "cuda")
+        self._buf: Optional[torch.Tensor] = None
+        self._base = 0
+        self.nbytes = 0
+
+    def reserve(self, T: int):
+        need = loader.workspace_bytes(T)
+        if self._buf is None or need > self.nbytes:
+            self._buf = torch.empty(need + 1024, dtype=torch.uint8, device=self.device)
+            self._base = (-self._buf.data_ptr()) % 1024
+            self.nbytes = need
+        return self
+
+    @property
+    def ptr(self) -> int:
+        return self._buf.data_ptr() + self._base
+
+    def view(self, offset: int, nbytes: int) -> torch.Tensor:
+        return self._buf[self._base + offset:self._base + offset + nbytes]
+
+
+_default_ws: Dict[int, Workspace] = {}
+
+
+def _default_workspace(device: torch.device) -> Workspace:
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    if idx not in _default_ws:
+        _default_ws[idx] = Workspace(torch.device("cuda", idx))
+    return _default_ws[idx]
+
+
+def _check(cond: bool, msg: str):
+    if not cond:
+        raise ValueError(msg)
+
+
+def _validate(routing_logits, routing_bias, hidden_states, hidden_states_scale, gemm1_weights, gemm1_weights_scale,
+              gemm2_weights, gemm2_weights_scale, output, device_inputs: bool):
+    T = routing_logits.shape[0]
+    _check(routing_logits.dtype == torch.float32 and tuple(routing_logits.shape) == (T, E_GLOBAL),
+           "routing_logits must be float32 [T, 256]")
+    _check(routing_bias.dtype == torch.bfloat16 and routing_bias.numel() == E_GLOBAL, "routing_bias must be bfloat16 [256]")
+    _check(hidden_states.dtype == torch.float8_e4m3fn and tuple(hidden_states.shape) == (T, H),
+           "hidden_states must be float8_e4m3fn [T, 7168]")
+    _check(hidden_states_scale.dtype == torch.float32 and tuple(hidden_states_scale.shape) == (H // BLOCK, T),
+           "hidden_states_scale must be float32 [56, T]")
+    _check(gemm1_weights.dtype == torch.float8_e4m3fn and tuple(gemm1_weights.shape) == (E_LOCAL, 2 * I, H),
+           "gemm1_weights must be float8_e4m3fn [32, 4096, 7168]")
+    _check(gemm1_weights_scale.dtype == torch.float32 and
+           tuple(gemm1_weights_scale.shape) == (E_LOCAL, 2 * I // BLOCK, H // BLOCK),
+           "gemm1_weights_scale must be float32 [32, 32, 56]")
+    _check(gemm2_weights.dtype == torch.float8_e4m3fn and tuple(gemm2_weights.shape) == (E_LOCAL, H, I),
+           "gemm2_weights must be float8_e4m3fn [32, 7168, 2048]")
+    _check(gemm2_weights_scale.dtype == torch.float32 and
+           tuple(gemm2_weights_scale.shape) == (E_LOCAL, H // BLOCK, I // BLOCK),
+           "gemm2_weights_scale must be float32 [32, 56, 16]")
+    _check(output.dtype == torch.bfloat16 and tuple(output.shape) == (T, H), "output must be bfloat16 [T, 7168]")
+    tensors = dict(routing_logits=routing_logits, routing_bias=routing_bias, hidden_states=hidden_states,
+                   hidden_states_scale=hidden_states_scale, gemm1_weights=gemm1_weights,
+                   gemm1_weights_scale=gemm1_weights_scale, gemm2_weights=gemm2_weights,
+                   gemm2_weights_scale=gemm2_weights_scale, output=output)
+    for name, t in tensors.items():
+        # size-1 dimensions make torch report odd strides for [56, 1]; numel-sized storage is what matters
+        _check(t.is_contiguous(), f"{name} must be contiguous")
+        on_device = name.startswith("gemm") or device_inputs
+        _check(t.is_cuda == on_device, f"{name} must live on the {'GPU' if on_device else 'host'}")
+    return T
+
+
+def run(routing_logits: torch.Tensor, routing_bias: torch.Tensor, hidden_states: torch.Tensor,
+        hidden_states_scale: torch.Tensor, gemm1_weights: torch.Tensor, gemm1_weights_scale: torch.Tensor,
+        gemm2_weights: torch.Tensor, gemm2_weights_scale: torch.Tensor, local_expert_offset: int,
+        routed_scaling_factor: float, output: Optional[torch.Tensor] = None,
+        workspace: Optional[Workspace] = None) -> torch.Tensor:
+    """The MoE shard, asynchronous on the current CUDA stream.  ``output`` (bf16
+    [T, 7168]) is fully overwritten and returned; it is allocated when omitted."""
+    if output is None:
+        output = torch.empty((routing_logits.shape[0], H), dtype=torch.bfloat16, device=hidden_states.device)
+    T = _validate(routing_logits, routing_bias, hidden_states, hidden_states_scale, gemm1_weights,
+                  gemm1_weights_scale, gemm2_weights, gemm2_weights_scale, output, device_inputs=True)
+    if T == 0:
+        return output
+    dev = hidden_states.device
+    ws = (workspace or _default_workspace(dev)).reserve(T)
+    with torch.cuda.device(dev):
+        stream = torch.cuda.current_stream(dev).cuda_stream
+        rc = loader.lib.moe_fp8_block_scale_run(
+            routing_logits.data_ptr(), routing_bias.data_ptr(), hidden_states.data_ptr(),
+            hidden_states_scale.data_ptr(), gemm1_weights.data_ptr(), gemm1_weights_scale.data_ptr(),
+            gemm2_weights.data_ptr(), gemm2_weights_scale.data_ptr(), int(T), int(local_expert_offset),
+            float(routed_scaling_factor), output.data_ptr(), ws.ptr, ws.nbytes, stream)
+    loader.check(rc)
+    return output
+
+
+def run_host(routing_logits, routing_bias, hidden_states, hidden_states_scale, gemm1_weights, gemm1_weights_scale,
+             gemm2_weights, gemm2_weights_scale, local_expert_offset: int, routed_scaling_factor: float,
+             output: torch.Tensor, workspace: Optional[Workspace] = None) -> torch.Tensor:
+    """Same operator for token-side tensors in (pinned) host memory: copies them
+    in, runs, copies ``output`` (a host tensor) back and waits."""
+    T = _validate(routing_logits, routing_bias, hidden_states, hidden_states_scale, gemm1_weights,
+                  gemm1_weights_scale, gemm2_weights, gemm2_weights_scale, output, device_inputs=False)
+    if T == 0:
+        return output
+    dev = gemm1_weights.device
+    ws = (workspace or _default_workspace(dev)).reserve(T)
+    with torch.cuda.device(dev):
+        stream = torch.cuda.current_stream(dev).cuda_stream
+        rc = loader.lib.moe_fp8_block_scale_run_host(
+            routing_logits.data_ptr(), routing_bias.data_ptr(), hidden_states.data_ptr(),
+            hidden_states_scale.data_ptr(), gemm1_weights.data_ptr(), gemm1_weights_scale.data_ptr(),
+            gemm2_weights.data_ptr(), gemm2_weights_scale.data_ptr(), int(T), int(local_expert_offset),
+            float(routed_scaling_factor), output.data_ptr(), ws.ptr, ws.nbytes, stream)
+    loader.check(rc)
+    return output
+
+
+def kernel_status(workspace: Optional[Workspace] = None, device=None) -> int:
+    """Waits for the current stream and returns the kernels' error bits (0 = none)."""
+    dev = torch.device(device if device is not None else "cuda")
+    ws = workspace or _default_workspace(dev)
+    st = ctypes.c_int(0)
+    with torch.cuda.device(ws.device):
+        rc = loader.lib.moe_fp8_block_scale_status(ws.ptr, torch.cuda.current_stream().cuda_stream, ctypes.byref(st))
+    if rc not in (loader.OK, loader.EKERNEL):
+        loader.check(rc)
+    return st.value
+
+
+def intermediates(T: int, workspace: Optional[Workspace] = None, device=None) -> dict:
+    """Host copies of the selection / permutation / per-stage arrays the last
+    call with ``T`` tokens left in the workspace (for parity tests)."""
+    dev = torch.device(device if device is not None else "cuda")
+    ws = workspace or _default_workspace(dev)
+    torch.cuda.synchronize(ws.device)
+    L = loader.layout(T)
+
+    def arr(off, nbytes, dtype, shape):
+        return ws.view(off, nbytes).view(dtype).reshape(shape)
+
+    sched_raw = ws.view(L.sched, ctypes.sizeof(loader.Sched)).cpu().numpy().tobytes()
+    sched = loader.Sched.from_buffer_copy(sched_raw)
+    n_sel, pad = sched.n_sel, sched.n_sel_pad
+    out = dict(
+        sched=sched, layout=L, n_sel=n_sel,
+        counts=torch.tensor(list(sched.counts)), offs=torch.tensor(list(sched.offs)),
+        topk_idx=arr(L.topk_idx, T * 8 * 4, torch.int32, (T, 8)).cpu(),
+        topk_w=arr(L.topk_w, T * 8 * 4, torch.float32, (T, 8)).cpu(),
+        local_mask=arr(L.local_mask, T * 4, torch.int32, (T,)).cpu(),
+        perm_token=arr(L.perm_token, n_sel * 4, torch.int32, (n_sel,)).cpu(),
+        perm_weight=arr(L.perm_weight, n_sel * 4, torch.float32, (n_sel,)).cpu(),
+        tok_rows=arr(L.tok_rows, T * 8 * 4, torch.int32, (T, 8)).cpu(),
+    )
+    if n_sel > 0:
+        g1 = arr(L.g1, sched.split1 * pad * 4096 * 4, torch.float32, (sched.split1, pad, 4096))
+        out["g1"] = g1.sum(dim=0)[:n_sel].cpu() if sched.split1 > 1 else g1[0, :n_sel].cpu()
+        o = arr(L.o, sched.split2 * pad * H * 4, torch.float32, (sched.split2, pad, H))
+        out["o"] = o.sum(dim=0)[:n_sel].cpu() if sched.split2 > 1 else o[0, :n_sel].cpu()
+        cq = arr(L.cq, L.n_terms * L.rows_cap * I, torch.float8_e4m3fn, (L.n_terms, L.rows_cap, I))[:, :n_sel]
+        cs = arr(L.c_scale, L.rows_cap * 16 * 4, torch.float32, (L.rows_cap, 16))[:n_sel]
+        c = cq.to(torch.float32).sum(dim=0).view(n_sel, 16, 128) * cs.unsqueeze(2)
+        out["c"] = c.view(n_sel, I).cpu()
+        out["a_packed"] = arr(L.a_packed, n_sel * H, torch.uint8, (n_sel, H)).cpu()
+    return out

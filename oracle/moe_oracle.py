@@ -1,0 +1,211 @@
+"""CPU restatement of the FP8 block-scale DeepSeek-V3 MoE shard definition.
+
+TEST INFRASTRUCTURE ONLY.  Nothing in the shipped package imports this file;
+it is the checker that the parity tests, the smoke test and the benchmark's
+``cpu_baseline`` leg compare the CUDA path against.
+
+It restates ``run`` of full-agent-pipeline/references/moe.py (the operator's
+PyTorch definition) with the same torch operations in the same order, so that
+on one machine the two are bit-identical; ``tests/golden/make_golden.py``
+checks exactly that against the unmodified reference file and stores the
+results as fixtures (parity pinned by those fixtures).  Two differences, none
+of them arithmetic:
+
+* it also returns what the definition computes on the way but does not return
+  (expert selection, per-expert token lists, the fp32 output before the bf16
+  cast), because the parity tests compare those bit for bit;
+* weights are dequantised one *active* expert at a time instead of all 32
+  up front (the definition materialises 5.6 GB of fp32 weights; the values
+  that take part in the result are the same).
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Callable, List, Optional
+
+import torch
+
+H = 7168
+I = 2048
+E_LOCAL = 32
+E_GLOBAL = 256
+BLOCK = 128
+TOP_K = 8
+N_GROUP = 8
+TOPK_GROUP = 4
+
+
+@dataclass
+class OracleResult:
+    output: torch.Tensor              # [T, H] bf16      (references/moe.py:202)
+    output_f32: torch.Tensor          # [T, H] fp32 before the cast
+    topk_idx: torch.Tensor            # [T, 8] int64, order as torch.topk(sorted=False) gives it
+    weights: torch.Tensor             # [T, 256] fp32 combination weights (zero where not selected)
+    counts: torch.Tensor              # [32] int64 tokens per local expert
+    offsets: torch.Tensor             # [33] int64 exclusive prefix of counts
+    perm_token: torch.Tensor          # [N_sel] int64: ascending token inside ascending local expert
+    perm_weight: torch.Tensor         # [N_sel] fp32
+    g1: List[Optional[torch.Tensor]] = field(default_factory=list)   # per local expert [Tk, 4096] fp32 or None
+    c: List[Optional[torch.Tensor]] = field(default_factory=list)    # per local expert [Tk, 2048] fp32 or None
+
+
+def dequant_activations(hidden_states: torch.Tensor, hidden_states_scale: torch.Tensor) -> torch.Tensor:
+    """references/moe.py:95-104: A = fp8 * scale, scale stored [H/128, T]."""
+    T = hidden_states.shape[0]
+    A_fp32 = hidden_states.to(torch.float32)
+    A_scale_TH = hidden_states_scale.to(torch.float32).permute(1, 0).contiguous()
+    A_scale_expanded = A_scale_TH.unsqueeze(-1).repeat(1, 1, BLOCK).reshape(T, H).contiguous()
+    return A_fp32 * A_scale_expanded
+
+
+def dequant_weight(w: torch.Tensor, s: torch.Tensor) -> torch.Tensor:
+    """references/moe.py:107-118 for one expert: W = fp8 * scale per 128x128 block."""
+    w32 = w.to(torch.float32)
+    s_exp = torch.repeat_interleave(s.to(torch.float32), BLOCK, dim=0)
+    s_exp = torch.repeat_interleave(s_exp, BLOCK, dim=1)
+    return w32 * s_exp
+
+
+def routing(routing_logits: torch.Tensor, routing_bias: torch.Tensor, routed_scaling_factor: float):
+    """references/moe.py:123-158.  Returns (topk_idx [T,8] int64, weights [T,256] fp32)."""
+    T = routing_logits.shape[0]
+    logits = routing_logits.to(torch.float32)
+    bias = routing_bias.to(torch.float32).reshape(-1)
+    s = 1.0 / (1.0 + torch.exp(-logits))
+    s_with_bias = s + bias
+    group_size = E_GLOBAL // N_GROUP
+    s_wb_grouped = s_with_bias.view(T, N_GROUP, group_size)
+    top2_vals, _ = torch.topk(s_wb_grouped, k=2, dim=2, largest=True, sorted=False)
+    group_scores = top2_vals.sum(dim=2)
+    _, group_idx = torch.topk(group_scores, k=TOPK_GROUP, dim=1, largest=True, sorted=False)
+    group_mask = torch.zeros_like(group_scores)
+    group_mask.scatter_(1, group_idx, 1.0)
+    score_mask = group_mask.unsqueeze(2).expand(T, N_GROUP, group_size).reshape(T, E_GLOBAL)
+    neg_inf = torch.finfo(torch.float32).min
+    scores_pruned = s_with_bias.masked_fill(score_mask == 0, neg_inf)
+    _, topk_idx = torch.topk(scores_pruned, k=TOP_K, dim=1, largest=True, sorted=False)
+    M = torch.zeros_like(s)
+    M.scatter_(1, topk_idx, 1.0)
+    weights = s * M
+    weights_sum = weights.sum(dim=1, keepdim=True) + 1e-20
+    weights = (weights / weights_sum) * routed_scaling_factor
+    return topk_idx, weights
+
+
+def selection_margins(routing_logits: torch.Tensor, routing_bias: torch.Tensor):
+    """Smallest relative gaps that decide the selection, per token: between the
+    4th and 5th group score and between the 8th and 9th pruned expert score.
+    A parity test that sees a selection mismatch uses this to tell a genuine
+    error from a one-ULP near-tie in the sigmoid."""
+    T = routing_logits.shape[0]
+    s = 1.0 / (1.0 + torch.exp(-routing_logits.to(torch.float32)))
+    swb = s + routing_bias.to(torch.float32).reshape(-1)
+    g = swb.view(T, N_GROUP, -1)
+    gs = torch.topk(g, 2, dim=2).values.sum(dim=2)
+    gsort = torch.sort(gs, dim=1, descending=True)
+    gap_g = gsort.values[:, TOPK_GROUP - 1] - gsort.values[:, TOPK_GROUP]
+    mask = torch.zeros_like(gs).scatter_(1, gsort.indices[:, :TOPK_GROUP], 1.0)
+    pruned = swb.masked_fill(mask.unsqueeze(2).expand(T, N_GROUP, E_GLOBAL // N_GROUP).reshape(T, E_GLOBAL) == 0,
+                             torch.finfo(torch.float32).min)
+    es = torch.sort(pruned, dim=1, descending=True).values
+    gap_e = es[:, TOP_K - 1] - es[:, TOP_K]
+    return gap_g, gap_e
+
+
+def run(routing_logits, routing_bias, hidden_states, hidden_states_scale,
+        expert_weights: Callable[[int], tuple], local_expert_offset: int,
+        routed_scaling_factor: float, keep_intermediates: bool = False) -> OracleResult:
+    """The operator.  ``expert_weights(le)`` returns that local expert's
+    ``(w13 e4m3 [4096,7168], s13 fp32 [32,56], w2 e4m3 [7168,2048], s2 fp32 [56,16])``;
+    it is called only for experts that receive a token (references/moe.py:168-200)."""
+    T = routing_logits.shape[0]
+    device = hidden_states.device
+    A = dequant_activations(hidden_states, hidden_states_scale)
+    topk_idx, weights = routing(routing_logits, routing_bias, routed_scaling_factor)
+
+    output = torch.zeros((T, H), dtype=torch.float32, device=device)
+    local_start = int(local_expert_offset)
+    counts = torch.zeros(E_LOCAL, dtype=torch.int64)
+    perm_token, perm_weight = [], []
+    g1_list: List[Optional[torch.Tensor]] = [None] * E_LOCAL
+    c_list: List[Optional[torch.Tensor]] = [None] * E_LOCAL
+    for le in range(E_LOCAL):
+        ge = local_start + le
+        if ge < 0 or ge >= E_GLOBAL:
+            continue
+        sel_mask_per_token = (topk_idx == ge).any(dim=1)
+        if not sel_mask_per_token.any():
+            continue
+        token_idx = torch.nonzero(sel_mask_per_token, as_tuple=False).squeeze(1)
+        counts[le] = token_idx.numel()
+        w13, s13, w2, s2 = expert_weights(le)
+        A_e = A.index_select(0, token_idx)
+        W13_e = dequant_weight(w13, s13)
+        G1 = A_e.matmul(W13_e.t())
+        del W13_e
+        X1 = G1[:, :I]
+        X2 = G1[:, I:]
+        silu_X2 = X2 / (1.0 + torch.exp(-X2))
+        C = silu_X2 * X1
+        W2_e = dequant_weight(w2, s2)
+        O = C.matmul(W2_e.t())
+        del W2_e
+        w_tok = weights.index_select(0, token_idx)[:, ge]
+        output.index_add_(0, token_idx, O * w_tok.unsqueeze(1))
+        perm_token.append(token_idx.cpu())
+        perm_weight.append(w_tok.cpu())
+        if keep_intermediates:
+            g1_list[le], c_list[le] = G1, C
+    offsets = torch.zeros(E_LOCAL + 1, dtype=torch.int64)
+    offsets[1:] = torch.cumsum(counts, 0)
+    pt = torch.cat(perm_token) if perm_token else torch.zeros(0, dtype=torch.int64)
+    pw = torch.cat(perm_weight) if perm_weight else torch.zeros(0, dtype=torch.float32)
+    return OracleResult(output.to(torch.bfloat16), output, topk_idx, weights, counts, offsets, pt, pw,
+                        g1_list, c_list)
+
+
+def run_full(routing_logits, routing_bias, hidden_states, hidden_states_scale,
+             gemm1_weights, gemm1_weights_scale, gemm2_weights, gemm2_weights_scale,
+             local_expert_offset: int, routed_scaling_factor: float, **kw) -> OracleResult:
+    """Same call shape as the definition (full [32,...] weight tensors)."""
+    def ew(le):
+        return gemm1_weights[le], gemm1_weights_scale[le], gemm2_weights[le], gemm2_weights_scale[le]
+    return run(routing_logits, routing_bias, hidden_states, hidden_states_scale, ew,
+               local_expert_offset, routed_scaling_factor, **kw)
+
+
+# ---------------------------------------------------------------------------------------------
+# Parity metrics shared by the tests, the smoke test and the benchmark's self-check.
+# ---------------------------------------------------------------------------------------------
+def selection_sets_equal(idx_a: torch.Tensor, idx_b: torch.Tensor) -> torch.Tensor:
+    """Per-token equality of two [T,8] expert selections as *sets*
+    (the definition asks torch.topk for sorted=False)."""
+    a = torch.sort(idx_a.to(torch.int64).cpu(), dim=1).values
+    b = torch.sort(idx_b.to(torch.int64).cpu(), dim=1).values
+    return (a == b).all(dim=1)
+
+
+def output_metrics(out_bf16: torch.Tensor, ref_bf16: torch.Tensor, ref_f32: Optional[torch.Tensor] = None) -> dict:
+    """max-abs error relative to the reference RMS, cosine, and a census of
+    elements that differ by exactly one bf16 step (a rounding flip of the
+    final cast) versus more."""
+    a = out_bf16.to(torch.float32).cpu().double()
+    b = ref_bf16.to(torch.float32).cpu().double()
+    rms = float(torch.sqrt((b * b).mean())) if b.numel() else 0.0
+    diff = (a - b).abs()
+    max_abs = float(diff.max()) if diff.numel() else 0.0
+    denom = float(a.norm() * b.norm())
+    cos = float((a * b).sum() / denom) if denom > 0 else 1.0
+    ai = out_bf16.cpu().view(torch.int16).to(torch.int32)
+    bi = ref_bf16.cpu().view(torch.int16).to(torch.int32)
+    # ordered-integer view of bf16 so that adjacent values differ by one
+    ao = torch.where(ai < 0, -(ai & 0x7FFF), ai)
+    bo = torch.where(bi < 0, -(bi & 0x7FFF), bi)
+    ulp = (ao - bo).abs()
+    m = dict(rms=rms, max_abs=max_abs, max_abs_over_rms=(max_abs / rms if rms > 0 else 0.0), cosine=cos,
+             n=int(a.numel()), n_diff=int((ulp > 0).sum()), n_one_step=int((ulp == 1).sum()),
+             n_multi_step=int((ulp > 1).sum()), max_steps=int(ulp.max()) if ulp.numel() else 0)
+    if ref_f32 is not None:
+        r = ref_f32.cpu().double()
+        m["max_abs_vs_f32_over_rms"] = float((a - r).abs().max()) / rms if rms > 0 else 0.0
+    return m
