@@ -102,6 +102,18 @@ typedef struct moe_b200_sched {
 
 int moe_fp8_block_scale_layout(int T, moe_b200_layout* out);
 
+/* Kernels launched by this library since it was loaded (all threads). */
+long long moe_fp8_block_scale_launch_count(void);
+
+/* Per-stage device timing for benchmarks: when enabled, CUDA events are
+ * recorded on the caller's stream between the six stages (route+permute, gather,
+ * GEMM1, SwiGLU split, GEMM2, combine).  ..._stage_times waits for the calling
+ * thread's last profiled call and writes the six durations in milliseconds.
+ * The reference has no counterpart; its per-kernel times were read from a profiler. */
+#define MOE_B200_STAGES 6
+int moe_fp8_block_scale_set_profiling(int enable);
+int moe_fp8_block_scale_stage_times(float* ms, int n);
+
 #ifdef __cplusplus
 }
 #endif

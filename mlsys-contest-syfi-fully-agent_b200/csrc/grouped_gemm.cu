@@ -15,15 +15,20 @@
 //   warp 0  producer: TMA (SWIZZLE_128B, no multicast) of one weight tile
 //           [128 rows x 128 K-bytes] and the token tile(s) [N_TILE x 128] per K-block
 //           into a ring of STAGES shared-memory stages.
-//   warp 1  issuer: one thread issues 4 (x kNTerms for GEMM2) tcgen05.mma
-//           kind::f8f6f4 M128 x N_TILE x K32 per K-block into one of two TMEM
-//           accumulator buffers, then commits to the stage's "empty" barrier and to
-//           the buffer's "full" barrier.
-//   warps 2-5  promotion + epilogue: tcgen05.ld the K-block partial, multiply by
-//           w_scale[e, m, kb] * b_scale[row, kb] and accumulate in registers (the
-//           scales are arbitrary fp32 per 128-block, so they cannot ride on the
-//           hardware's power-of-two block scaling); after the last K-block store the
-//           fp32 tile transposed, i.e. token-major [row, m].
+//   warp 1  issuer: one thread issues the tcgen05.mma kind::f8f6f4 (M128, K32) of a
+//           K-block into its own TMEM columns.  For GEMM2 the kNTerms e4m3 planes of
+//           the token operand sit back to back in shared memory and, while they fit
+//           N <= 256, are consumed as ONE operand of N = kNTerms * N_TILE rows, so the
+//           weight tile is read from shared memory once per K32 step, not once per term.
+//           G consecutive K-blocks form a hand-off group with one "full" barrier;
+//           NBUF groups rotate through TMEM so that the hand-off latency between the
+//           tensor core and the promotion warps is hidden.
+//   warps 2-9  promotion + epilogue (two warps per TMEM lane quarter, each owning half
+//           of the token columns): tcgen05.ld the partials of a group, release the TMEM
+//           buffer, multiply by w_scale[e, m, kb] * b_scale[row, kb] and accumulate in
+//           registers (the scales are arbitrary fp32 per 128-block, so they cannot ride
+//           on the hardware's power-of-two block scaling); after the last K-block store
+//           the fp32 tile transposed, i.e. token-major [row, m].
 //
 // Work items (expert, weight-row tile, K-split, token tile) are decoded from the
 // device-resident schedule; CTAs are persistent and take items round-robin.
@@ -36,32 +41,49 @@ namespace moe {
 
 namespace {
 
+constexpr int kEpiWarps = 8;
+constexpr int kThreads = 64 + kEpiWarps * 32;   // producer warp + issuer warp + epilogue warps
+
 template <int GEMM, int N_TILE>
 struct Cfg {
   static constexpr int KB = GEMM == 1 ? kKB1 : kKB2;
   static constexpr int MT = GEMM == 1 ? kMT1 : kMT2;
   static constexpr int M_TOTAL = MT * 128;
   static constexpr int NTERMS = GEMM == 1 ? 1 : kNTerms;
+  static constexpr bool STACK = NTERMS > 1 && NTERMS * N_TILE <= 256;   // planes consumed as one N operand
+  static constexpr int N_MMA = STACK ? NTERMS * N_TILE : N_TILE;        // UMMA N
+  static constexpr int MMA_PER_K4 = STACK ? 1 : NTERMS;
+  static constexpr int PLANES = STACK ? NTERMS : 1;                     // column planes the epilogue sums
+  static constexpr int KB_COLS = N_MMA;                                 // TMEM columns of one K-block partial
+  static constexpr int G = KB_COLS <= 16 ? 4 : KB_COLS <= 64 ? 2 : 1;   // K-blocks per hand-off
+  static constexpr int NBUF_FIT = 512 / (G * KB_COLS);
+  static constexpr int NBUF = NBUF_FIT > 4 ? 4 : NBUF_FIT;
+  static constexpr int TMEM_USED = NBUF * G * KB_COLS;
+  static constexpr int TMEM_COLS = TMEM_USED <= 32 ? 32 : TMEM_USED <= 64 ? 64 : TMEM_USED <= 128 ? 128
+                                   : TMEM_USED <= 256 ? 256 : 512;
+  static constexpr int CPW = N_TILE / 2;                                // token columns per epilogue warp
   static constexpr int A_BYTES = 128 * 128;
   static constexpr int B_BYTES = N_TILE * 128;
   static constexpr int STAGE_BYTES = A_BYTES + NTERMS * B_BYTES;
-  static constexpr int SC_BYTES = KB * N_TILE * 4;
+  static constexpr int SC_BUFS = N_TILE <= 32 ? 2 : 1;                  // scale-product tables
+  static constexpr int SC_BYTES = SC_BUFS * KB * N_TILE * 4;
   static constexpr int AUX_BYTES = 1024;
   static constexpr int BUDGET = 227 * 1024 - 1024;   // 1 KB slack for the 1024-byte alignment of the ring
   static constexpr int STAGES_FIT = (BUDGET - SC_BYTES - AUX_BYTES) / STAGE_BYTES;
   static constexpr int STAGES = STAGES_FIT > 10 ? 10 : STAGES_FIT;
   static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + SC_BYTES + AUX_BYTES + 1024;
-  static constexpr int TMEM_COLS = 2 * N_TILE < 32 ? 32 : 2 * N_TILE;
   static_assert(STAGES >= 2, "ring too small");
-  static_assert((TMEM_COLS & (TMEM_COLS - 1)) == 0, "TMEM columns must be a power of two");
+  static_assert(NBUF >= 2 && TMEM_USED <= 512, "TMEM budget");
+  static_assert(N_MMA % 16 == 0 && N_MMA >= 16 && N_MMA <= 256, "invalid UMMA N for M = 128");
+  static_assert(SMEM_BYTES > 116 * 1024, "one CTA per SM is assumed (TMEM is allocated without contention)");
 };
 
 struct Aux {
   uint64_t full[10];
   uint64_t empty[10];
-  uint64_t tfull[2];
-  uint64_t tempty[2];
-  uint64_t esync;          // bounded replacement for a named barrier among the 128 epilogue threads
+  uint64_t tfull[4];
+  uint64_t tempty[4];
+  uint64_t esync;          // bounded replacement for a named barrier among the epilogue threads
   uint32_t tmem_base;
   int abort;
   int prefix[kELocal + 1];
@@ -77,12 +99,12 @@ template <int GEMM, int N_TILE>
 __device__ __forceinline__ Item decode_item(int i, int split, const Aux* aux) {
   using C = Cfg<GEMM, N_TILE>;
   const int per = C::MT * split;
+  // largest e with prefix[e] * per <= i (experts without tiles repeat the prefix value, so
+  // the largest such e is the one that owns tile i)
   int e = 0;
 #pragma unroll 1
   for (int k = 16; k > 0; k >>= 1)
     if (e + k < kELocal && aux->prefix[e + k] * per <= i) e += k;
-  // skip experts without tiles that share the same prefix value
-  while (e < kELocal - 1 && aux->prefix[e + 1] * per <= i) ++e;
   int r = i - aux->prefix[e] * per;
   const int tiles_e = aux->prefix[e + 1] - aux->prefix[e];
   const int n = r % tiles_e;
@@ -99,13 +121,26 @@ __device__ __forceinline__ Item decode_item(int i, int split, const Aux* aux) {
   return it;
 }
 
+// CPW fp32 columns of this warp's 32 TMEM lanes -> registers.
+template <int CPW>
+__device__ __forceinline__ void tmem_ld_cols(uint32_t taddr, float* v) {
+  if constexpr (CPW == 8) {
+    tmem_ld8(taddr, v);
+  } else if constexpr (CPW == 16) {
+    tmem_ld16(taddr, v);
+  } else {
+#pragma unroll
+    for (int c = 0; c < CPW / 32; ++c) tmem_ld32(taddr + c * 32, v + c * 32);
+  }
+}
+
 template <int GEMM, int N_TILE>
-__global__ void __launch_bounds__(192, 1)
+__global__ void __launch_bounds__(kThreads, 1)
 grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_b, GemmArgs a) {
   using C = Cfg<GEMM, N_TILE>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  float* sc = reinterpret_cast<float*>(smem + C::STAGES * C::STAGE_BYTES);
+  float* sc_base = reinterpret_cast<float*>(smem + C::STAGES * C::STAGE_BYTES);
   Aux* aux = reinterpret_cast<Aux*>(smem + C::STAGES * C::STAGE_BYTES + C::SC_BYTES);
 
   const int warp = threadIdx.x >> 5;
@@ -125,11 +160,11 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
       mbar_init(smem_u32(&aux->full[s]), 1);
       mbar_init(smem_u32(&aux->empty[s]), 1);
     }
-    for (int b = 0; b < 2; ++b) {
+    for (int b = 0; b < C::NBUF; ++b) {
       mbar_init(smem_u32(&aux->tfull[b]), 1);
-      mbar_init(smem_u32(&aux->tempty[b]), 4);
+      mbar_init(smem_u32(&aux->tempty[b]), kEpiWarps);
     }
-    mbar_init(smem_u32(&aux->esync), 128);
+    mbar_init(smem_u32(&aux->esync), kEpiWarps * 32);
     fence_mbar_init();
     tma_prefetch_desc(&tm_w);
     tma_prefetch_desc(&tm_b);
@@ -168,52 +203,60 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
   } else if (warp == 1) {
     // ------------------------------------------------------------------ UMMA issuer
     if (lane == 0) {
-      constexpr uint32_t idesc = umma_idesc_e4m3(128, N_TILE);
-      uint32_t it = 0;
+      constexpr uint32_t idesc = umma_idesc_e4m3(128, C::N_MMA);
+      uint32_t it = 0, gi = 0;
       bool ok = true;
       for (int i = blockIdx.x; ok && i < items; i += gridDim.x) {
         const Item w = decode_item<GEMM, N_TILE>(i, split, aux);
-        for (int kb = w.kb0; kb < w.kb1; ++kb, ++it) {
-          const uint32_t stage = it % C::STAGES, ph = (it / C::STAGES) & 1u;
-          const uint32_t buf = it & 1u, bph = (it >> 1) & 1u;
+        const int nkb = w.kb1 - w.kb0;
+        for (int kbl = 0; ok && kbl < nkb; kbl += C::G, ++gi) {
+          const uint32_t buf = gi % C::NBUF, bph = (gi / C::NBUF) & 1u;
           if (!mbar_wait(smem_u32(&aux->tempty[buf]), bph ^ 1u, abort_flag)) { ok = false; break; }
-          if (!mbar_wait(smem_u32(&aux->full[stage]), ph, abort_flag)) { ok = false; break; }
-          tc_fence_after_sync();
-          const uint32_t sa = smem_u32(smem + stage * C::STAGE_BYTES);
-          const uint64_t adesc = umma_desc_k_sw128(sa);
-          const uint32_t d = tmem_base + buf * N_TILE;
+          const int gsize = min(C::G, nkb - kbl);
+          for (int g = 0; g < gsize; ++g, ++it) {
+            const uint32_t stage = it % C::STAGES, ph = (it / C::STAGES) & 1u;
+            if (!mbar_wait(smem_u32(&aux->full[stage]), ph, abort_flag)) { ok = false; break; }
+            tc_fence_after_sync();
+            const uint32_t sa = smem_u32(smem + stage * C::STAGE_BYTES);
+            const uint64_t adesc = umma_desc_k_sw128(sa);
+            const uint32_t d = tmem_base + buf * (C::G * C::KB_COLS) + g * C::KB_COLS;
 #pragma unroll
-          for (int t = 0; t < C::NTERMS; ++t) {
-            const uint64_t bdesc = umma_desc_k_sw128(sa + C::A_BYTES + t * C::B_BYTES);
+            for (int t = 0; t < C::MMA_PER_K4; ++t) {
+              const uint64_t bdesc = umma_desc_k_sw128(sa + C::A_BYTES + t * C::B_BYTES);
 #pragma unroll
-            for (int k4 = 0; k4 < 4; ++k4)   // +32 bytes of K inside the 128-byte swizzle atom = +2 encoded units
-              umma_f8(d, adesc + 2 * k4, bdesc + 2 * k4, idesc, (t | k4) != 0 ? 1u : 0u);
+              for (int k4 = 0; k4 < 4; ++k4)   // +32 bytes of K inside the 128-byte swizzle atom = +2 encoded units
+                umma_f8(d, adesc + 2 * k4, bdesc + 2 * k4, idesc, (t | k4) != 0 ? 1u : 0u);
+            }
+            umma_commit(smem_u32(&aux->empty[stage]));
           }
-          umma_commit(smem_u32(&aux->empty[stage]));
-          umma_commit(smem_u32(&aux->tfull[buf]));
+          if (ok) umma_commit(smem_u32(&aux->tfull[buf]));
         }
       }
     }
   } else {
-    // ------------------------------------------------------------------ promotion + epilogue (warps 2..5)
+    // ------------------------------------------------------------------ promotion + epilogue (warps 2..9)
     const int q = warp & 3;                       // TMEM lane quarter this warp may access
-    const int etid = threadIdx.x - 64;            // 0..127
+    const int h = (warp - 2) >> 2;                // which half of the token columns
+    const int etid = threadIdx.x - 64;            // 0..255
     const uint32_t lane_addr = static_cast<uint32_t>(q * 32) << 16;
-    uint32_t it = 0, eph = 0;
+    uint32_t gi = 0, eph = 0, nitem = 0;
     bool ok = true;
-    // all 128 epilogue threads meet here; bounded like every other wait in this kernel
+    // all epilogue threads meet here; bounded like every other wait in this kernel
     auto epi_sync = [&]() {
       mbar_arrive(smem_u32(&aux->esync));
       if (!mbar_wait(smem_u32(&aux->esync), eph, abort_flag)) ok = false;
       eph ^= 1u;
     };
-    for (int i = blockIdx.x; ok && i < items; i += gridDim.x) {
+    for (int i = blockIdx.x; ok && i < items; i += gridDim.x, ++nitem) {
       const Item w = decode_item<GEMM, N_TILE>(i, split, aux);
       const int nkb = w.kb1 - w.kb0;
-      epi_sync();   // the previous item's scale products are no longer being read
-      if (!ok) break;
+      float* sc = sc_base + (C::SC_BUFS == 2 ? (nitem & 1u) * (C::KB * N_TILE) : 0);
+      if (C::SC_BUFS == 1) {
+        epi_sync();   // the previous item's scale products are no longer being read
+        if (!ok) break;
+      }
       const float* ws = a.w_scale + (static_cast<size_t>(w.e) * C::MT + w.m) * C::KB;
-      for (int idx = etid; idx < nkb * N_TILE; idx += 128) {
+      for (int idx = etid; idx < nkb * N_TILE; idx += kEpiWarps * 32) {
         const int kbl = idx / N_TILE, j = idx % N_TILE, kb = w.kb0 + kbl;
         float bs = 0.0f;
         if (j < w.valid) {
@@ -225,39 +268,55 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
       epi_sync();
       if (!ok) break;
 
-      float acc[N_TILE];
+      float acc[C::CPW];
 #pragma unroll
-      for (int j = 0; j < N_TILE; ++j) acc[j] = 0.0f;
+      for (int j = 0; j < C::CPW; ++j) acc[j] = 0.0f;
 
-      for (int kbl = 0; kbl < nkb; ++kbl, ++it) {
-        const uint32_t buf = it & 1u, bph = (it >> 1) & 1u;
+      for (int kbl = 0; kbl < nkb; kbl += C::G, ++gi) {
+        const uint32_t buf = gi % C::NBUF, bph = (gi / C::NBUF) & 1u;
+        const int gsize = min(C::G, nkb - kbl);
         if (!mbar_wait(smem_u32(&aux->tfull[buf]), bph, abort_flag)) { ok = false; break; }
         tc_fence_after_sync();
-        const uint32_t taddr = tmem_base + lane_addr + buf * N_TILE;
-        const float4* scv = reinterpret_cast<const float4*>(sc + kbl * N_TILE);
+        const uint32_t taddr = tmem_base + lane_addr + buf * (C::G * C::KB_COLS) + h * C::CPW;
+        float v[C::G][C::PLANES][C::CPW];
 #pragma unroll
-        for (int c = 0; c < N_TILE / 16; ++c) {
-          float v[16];
-          tmem_ld16(taddr + c * 16, v);
-          tmem_wait_ld();
+        for (int g = 0; g < C::G; ++g)
+          if (g < gsize) {
 #pragma unroll
-          for (int u = 0; u < 4; ++u) {
-            const float4 f = scv[c * 4 + u];
-            acc[c * 16 + u * 4 + 0] = fmaf(v[u * 4 + 0], f.x, acc[c * 16 + u * 4 + 0]);
-            acc[c * 16 + u * 4 + 1] = fmaf(v[u * 4 + 1], f.y, acc[c * 16 + u * 4 + 1]);
-            acc[c * 16 + u * 4 + 2] = fmaf(v[u * 4 + 2], f.z, acc[c * 16 + u * 4 + 2]);
-            acc[c * 16 + u * 4 + 3] = fmaf(v[u * 4 + 3], f.w, acc[c * 16 + u * 4 + 3]);
+            for (int p = 0; p < C::PLANES; ++p) tmem_ld_cols<C::CPW>(taddr + g * C::KB_COLS + p * N_TILE, v[g][p]);
           }
-        }
+        tmem_wait_ld();
         tc_fence_before_sync();
         __syncwarp();
-        if (lane == 0) mbar_arrive(smem_u32(&aux->tempty[buf]));
+        if (lane == 0) mbar_arrive(smem_u32(&aux->tempty[buf]));   // partials are in registers: free the buffer
+#pragma unroll
+        for (int g = 0; g < C::G; ++g)
+          if (g < gsize) {
+            const float4* scv = reinterpret_cast<const float4*>(sc + (kbl + g) * N_TILE + h * C::CPW);
+#pragma unroll
+            for (int u = 0; u < C::CPW / 4; ++u) {
+              const float4 f = scv[u];
+              float s4[4];
+#pragma unroll
+              for (int x = 0; x < 4; ++x) {
+                float s = v[g][C::PLANES - 1][u * 4 + x];
+#pragma unroll
+                for (int p = C::PLANES - 2; p >= 0; --p) s += v[g][p][u * 4 + x];   // smallest terms first
+                s4[x] = s;
+              }
+              acc[u * 4 + 0] = fmaf(s4[0], f.x, acc[u * 4 + 0]);
+              acc[u * 4 + 1] = fmaf(s4[1], f.y, acc[u * 4 + 1]);
+              acc[u * 4 + 2] = fmaf(s4[2], f.z, acc[u * 4 + 2]);
+              acc[u * 4 + 3] = fmaf(s4[3], f.w, acc[u * 4 + 3]);
+            }
+          }
       }
       if (!ok) break;
-      float* out = a.out + (static_cast<size_t>(w.s) * n_sel_pad + w.row0) * C::M_TOTAL + w.m * 128 + q * 32 + lane;
+      float* out = a.out + (static_cast<size_t>(w.s) * n_sel_pad + w.row0 + h * C::CPW) * C::M_TOTAL + w.m * 128 +
+                   q * 32 + lane;
 #pragma unroll
-      for (int j = 0; j < N_TILE; ++j)
-        if (j < w.valid) out[static_cast<size_t>(j) * C::M_TOTAL] = acc[j];
+      for (int j = 0; j < C::CPW; ++j)
+        if (h * C::CPW + j < w.valid) out[static_cast<size_t>(j) * C::M_TOTAL] = acc[j];
     }
   }
 
@@ -274,7 +333,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
 template <int GEMM, int N_TILE>
 int launch_one(const CUtensorMap& tm_w, const CUtensorMap& tm_b, const GemmArgs& a, int ctas, cudaStream_t stream) {
   using C = Cfg<GEMM, N_TILE>;
-  grouped_gemm_kernel<GEMM, N_TILE><<<ctas, 192, C::SMEM_BYTES, stream>>>(tm_w, tm_b, a);
+  grouped_gemm_kernel<GEMM, N_TILE><<<ctas, kThreads, C::SMEM_BYTES, stream>>>(tm_w, tm_b, a);
   return static_cast<int>(cudaGetLastError());
 }
 

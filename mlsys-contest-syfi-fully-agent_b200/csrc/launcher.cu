@@ -7,6 +7,7 @@
 #include <cuda.h>
 #include <cuda_runtime.h>
 
+#include <atomic>
 #include <cstdlib>
 #include <cstring>
 #include <mutex>
@@ -18,6 +19,28 @@ namespace moe {
 namespace {
 
 thread_local int g_last_cuda_error = 0;
+
+// Optional per-stage timing (CUDA events recorded on the caller's stream between the
+// stages) and a count of the kernels this library has launched.
+constexpr int kStages = 6;   // route+permute, gather, GEMM1, SwiGLU split, GEMM2, combine
+std::atomic<long long> g_launches{0};
+std::atomic<int> g_profiling{0};
+struct StageEvents {
+  cudaEvent_t ev[kStages + 1];
+  bool created = false;
+  bool recorded = false;
+};
+thread_local StageEvents g_events;
+
+void stage_mark(int i, cudaStream_t stream) {
+  if (!g_profiling.load(std::memory_order_relaxed)) return;
+  if (!g_events.created) {
+    for (auto& e : g_events.ev) cudaEventCreate(&e);
+    g_events.created = true;
+  }
+  cudaEventRecord(g_events.ev[i], stream);
+  if (i == kStages) g_events.recorded = true;
+}
 
 #define MOE_CUDA(expr)                                   \
   do {                                                   \
@@ -223,32 +246,45 @@ extern "C" int moe_fp8_block_scale_run(const float* routing_logits, const uint16
                local_mask};
   PermuteArgs pa{T, local_expert_offset, n_tile, ctas, L.rows_cap, L.slab_rows, local_mask, topk_idx, topk_w,
                  sched, perm_token, perm_weight, tok_rows};
+  stage_mark(0, stream);
   launch_route_permute(ra, pa, stream);
   MOE_CUDA(cudaGetLastError());
+  g_launches += T <= 256 ? 1 : 2;
+  stage_mark(1, stream);
 
   GatherArgs ga{sched, perm_token, hidden_states, a_packed};
   launch_gather_rows(ga, T, stream);
   MOE_CUDA(cudaGetLastError());
+  g_launches += 1;
+  stage_mark(2, stream);
 
   GemmArgs g1a{sched, gemm1_weights_scale, hidden_states_scale, perm_token, T, 0, g1};
   if ((rc = launch_grouped_gemm(1, n_tile, tm_w13, tm_a, g1a, ctas, stream))) {
     g_last_cuda_error = rc;
     return MOE_B200_ECUDA;
   }
+  g_launches += 1;
+  stage_mark(3, stream);
 
   SwigluArgs sa{sched, g1, cq, c_scale, L.rows_cap};
   launch_swiglu_split(sa, T, stream);
   MOE_CUDA(cudaGetLastError());
+  g_launches += 1;
+  stage_mark(4, stream);
 
   GemmArgs g2a{sched, gemm2_weights_scale, c_scale, nullptr, T, L.rows_cap, o};
   if ((rc = launch_grouped_gemm(2, n_tile, tm_w2, tm_c, g2a, ctas, stream))) {
     g_last_cuda_error = rc;
     return MOE_B200_ECUDA;
   }
+  g_launches += 1;
+  stage_mark(5, stream);
 
   CombineArgs ca{sched, o, local_mask, tok_rows, perm_weight, output, T};
   launch_combine(ca, stream);
   MOE_CUDA(cudaGetLastError());
+  g_launches += 1;
+  stage_mark(6, stream);
   return MOE_B200_OK;
 }
 
@@ -294,4 +330,19 @@ extern "C" int moe_fp8_block_scale_status(const void* workspace, void* stream_v,
   const WorkspaceLayout L = make_layout(1);
   MOE_CUDA(cudaMemcpy(status, static_cast<const uint8_t*>(workspace) + L.sched, sizeof(int), cudaMemcpyDeviceToHost));
   return *status == 0 ? MOE_B200_OK : MOE_B200_EKERNEL;
+}
+
+extern "C" long long moe_fp8_block_scale_launch_count(void) { return g_launches.load(); }
+
+extern "C" int moe_fp8_block_scale_set_profiling(int enable) {
+  g_profiling.store(enable ? 1 : 0);
+  return MOE_B200_OK;
+}
+
+extern "C" int moe_fp8_block_scale_stage_times(float* ms, int n) {
+  if (!ms || n < kStages) return MOE_B200_EINVAL;
+  if (!g_events.recorded) return MOE_B200_EINVAL;
+  MOE_CUDA(cudaEventSynchronize(g_events.ev[kStages]));
+  for (int i = 0; i < kStages; ++i) MOE_CUDA(cudaEventElapsedTime(&ms[i], g_events.ev[i], g_events.ev[i + 1]));
+  return MOE_B200_OK;
 }

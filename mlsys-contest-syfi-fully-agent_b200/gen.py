@@ -96,13 +96,19 @@ def normal(seed: int, stream: int, start: int, count: int, device, chunk: int = 
     return out
 
 
+def _div_ieee(x: torch.Tensor, d: float) -> torch.Tensor:
+    """x / d with a correctly rounded division on every device (CUDA turns division by a
+    Python scalar into a multiplication by its reciprocal, which differs in the last bit)."""
+    return x / torch.full_like(x, d)
+
+
 def quant_1x128(x: torch.Tensor):
     """Per-row 1x128 block quantisation of ``x`` [R, C] (C % 128 == 0) to e4m3.
     Returns (q fp8 [R, C], scale fp32 [R, C/128]), scale = amax/448."""
     R, C = x.shape
     xb = x.view(R, C // BLOCK, BLOCK)
     amax = xb.abs().amax(dim=2).clamp_min(1e-10)
-    scale = amax / FP8_MAX
+    scale = _div_ieee(amax, FP8_MAX)
     q = (xb / scale.unsqueeze(2)).to(torch.float8_e4m3fn).view(R, C)
     return q, scale
 
@@ -113,7 +119,7 @@ def quant_128x128(w: torch.Tensor):
     R, C = w.shape
     wb = w.view(R // BLOCK, BLOCK, C // BLOCK, BLOCK)
     amax = wb.abs().amax(dim=(1, 3)).clamp_min(1e-10)
-    scale = amax / FP8_MAX
+    scale = _div_ieee(amax, FP8_MAX)
     q = (wb / scale[:, None, :, None]).to(torch.float8_e4m3fn).view(R, C)
     return q, scale
 

@@ -23,7 +23,11 @@ EXPORTS = [
     "moe_fp8_block_scale_status",
     "moe_fp8_block_scale_last_cuda_error",
     "moe_fp8_block_scale_layout",
+    "moe_fp8_block_scale_launch_count",
+    "moe_fp8_block_scale_set_profiling",
+    "moe_fp8_block_scale_stage_times",
 ]
+STAGES = ("route_permute", "gather", "gemm1", "swiglu_split", "gemm2", "combine")
 
 
 class Layout(ctypes.Structure):
@@ -69,10 +73,30 @@ def _load() -> ctypes.CDLL:
     lib.moe_fp8_block_scale_last_cuda_error.argtypes = []
     lib.moe_fp8_block_scale_layout.restype = i32
     lib.moe_fp8_block_scale_layout.argtypes = [i32, ctypes.POINTER(Layout)]
+    lib.moe_fp8_block_scale_launch_count.restype = ctypes.c_longlong
+    lib.moe_fp8_block_scale_launch_count.argtypes = []
+    lib.moe_fp8_block_scale_set_profiling.restype = i32
+    lib.moe_fp8_block_scale_set_profiling.argtypes = [i32]
+    lib.moe_fp8_block_scale_stage_times.restype = i32
+    lib.moe_fp8_block_scale_stage_times.argtypes = [ctypes.POINTER(f32), i32]
     return lib
 
 
 lib = _load()
+
+
+def launch_count() -> int:
+    return int(lib.moe_fp8_block_scale_launch_count())
+
+
+def set_profiling(enable: bool):
+    check(lib.moe_fp8_block_scale_set_profiling(1 if enable else 0))
+
+
+def stage_times_ms() -> dict:
+    buf = (ctypes.c_float * len(STAGES))()
+    check(lib.moe_fp8_block_scale_stage_times(buf, len(STAGES)))
+    return dict(zip(STAGES, [float(x) for x in buf]))
 
 
 def check(code: int):

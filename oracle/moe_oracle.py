@@ -185,6 +185,15 @@ def selection_sets_equal(idx_a: torch.Tensor, idx_b: torch.Tensor) -> torch.Tens
     return (a == b).all(dim=1)
 
 
+def bf16_steps(a_bf16: torch.Tensor, b_bf16: torch.Tensor) -> torch.Tensor:
+    """Number of representable bf16 values between corresponding elements (0 = equal, 1 = adjacent)."""
+    ai = a_bf16.cpu().contiguous().view(torch.int16).to(torch.int32)
+    bi = b_bf16.cpu().contiguous().view(torch.int16).to(torch.int32)
+    ao = torch.where(ai < 0, -(ai & 0x7FFF), ai)
+    bo = torch.where(bi < 0, -(bi & 0x7FFF), bi)
+    return (ao - bo).abs()
+
+
 def output_metrics(out_bf16: torch.Tensor, ref_bf16: torch.Tensor, ref_f32: Optional[torch.Tensor] = None) -> dict:
     """max-abs error relative to the reference RMS, cosine, and a census of
     elements that differ by exactly one bf16 step (a rounding flip of the
@@ -196,12 +205,7 @@ def output_metrics(out_bf16: torch.Tensor, ref_bf16: torch.Tensor, ref_f32: Opti
     max_abs = float(diff.max()) if diff.numel() else 0.0
     denom = float(a.norm() * b.norm())
     cos = float((a * b).sum() / denom) if denom > 0 else 1.0
-    ai = out_bf16.cpu().view(torch.int16).to(torch.int32)
-    bi = ref_bf16.cpu().view(torch.int16).to(torch.int32)
-    # ordered-integer view of bf16 so that adjacent values differ by one
-    ao = torch.where(ai < 0, -(ai & 0x7FFF), ai)
-    bo = torch.where(bi < 0, -(bi & 0x7FFF), bi)
-    ulp = (ao - bo).abs()
+    ulp = bf16_steps(out_bf16, ref_bf16)
     m = dict(rms=rms, max_abs=max_abs, max_abs_over_rms=(max_abs / rms if rms > 0 else 0.0), cosine=cos,
              n=int(a.numel()), n_diff=int((ulp > 0).sum()), n_one_step=int((ulp == 1).sum()),
              n_multi_step=int((ulp > 1).sum()), max_steps=int(ulp.max()) if ulp.numel() else 0)
