@@ -85,6 +85,7 @@ typedef struct moe_b200_layout {
   uint64_t perm_weight;  /* f32 [n_sel]                                      */
   uint64_t tok_rows;     /* i32 [T, 8] rows of each token, ascending expert  */
   uint64_t a_packed;     /* e4m3 [rows_cap, 7168] permuted activations       */
+  uint64_t a_scale_rows; /* f32 [rows_cap, 56] block scales of each permuted row  */
   uint64_t g1;           /* f32 [split1][n_sel_pad, 4096] GEMM1 slabs        */
   uint64_t cq;           /* e4m3 [n_terms][rows_cap, 2048] SwiGLU planes     */
   uint64_t c_scale;      /* f32 [rows_cap, 16]                               */

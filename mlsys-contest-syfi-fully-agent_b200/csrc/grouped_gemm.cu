@@ -39,6 +39,14 @@
 
 namespace moe {
 
+#ifdef MOE_TRACE
+// Debug build only: per-role time stamps of CTA 0, [gemm][role][slot].
+__device__ unsigned long long g_moe_trace[2][4][256];
+#define TRACE(role, slot) do { if (blockIdx.x == 0 && (slot) < 256) g_moe_trace[GEMM - 1][role][slot] = static_cast<unsigned long long>(clock64()); } while (0)
+#else
+#define TRACE(role, slot) do { } while (0)
+#endif
+
 namespace {
 
 constexpr int kEpiWarps = 8;
@@ -145,15 +153,10 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
+  if (threadIdx.x == 0) TRACE(3, 0);
+  griddep_launch_dependents();
   MoeSched* sched = a.sched;
-  const int items = GEMM == 1 ? sched->items1 : sched->items2;
-  const int split = GEMM == 1 ? sched->split1 : sched->split2;
-  const int n_sel_pad = sched->n_sel_pad;
-
-  if (threadIdx.x <= kELocal) {
-    aux->prefix[threadIdx.x] = sched->tile_prefix[threadIdx.x];
-    aux->offs[threadIdx.x] = sched->offs[threadIdx.x];
-  }
+  // everything that does not depend on earlier kernels first: barriers, descriptors, TMEM
   if (threadIdx.x == 0) {
     aux->abort = 0;
     for (int s = 0; s < C::STAGES; ++s) {
@@ -173,11 +176,20 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
     tmem_alloc(smem_u32(&aux->tmem_base), C::TMEM_COLS);
     tmem_relinquish();
   }
+  griddep_wait();   // the schedule, the operands and the output slabs belong to earlier kernels until here
+  const int items = GEMM == 1 ? sched->items1 : sched->items2;
+  const int split = GEMM == 1 ? sched->split1 : sched->split2;
+  const int n_sel_pad = sched->n_sel_pad;
+  if (threadIdx.x <= kELocal) {
+    aux->prefix[threadIdx.x] = sched->tile_prefix[threadIdx.x];
+    aux->offs[threadIdx.x] = sched->offs[threadIdx.x];
+  }
   tc_fence_before_sync();
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = aux->tmem_base;
   volatile int* abort_flag = &aux->abort;
+  if (threadIdx.x == 0) TRACE(3, 1);
 
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
@@ -190,6 +202,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
         for (int kb = w.kb0; kb < w.kb1; ++kb, ++it) {
           const uint32_t stage = it % C::STAGES, ph = (it / C::STAGES) & 1u;
           if (!mbar_wait(smem_u32(&aux->empty[stage]), ph ^ 1u, abort_flag)) { ok = false; break; }
+          TRACE(0, it);
           const uint32_t bar = smem_u32(&aux->full[stage]);
           mbar_arrive_expect_tx(bar, C::STAGE_BYTES);
           const uint32_t dst = smem_u32(smem + stage * C::STAGE_BYTES);
@@ -216,6 +229,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
           for (int g = 0; g < gsize; ++g, ++it) {
             const uint32_t stage = it % C::STAGES, ph = (it / C::STAGES) & 1u;
             if (!mbar_wait(smem_u32(&aux->full[stage]), ph, abort_flag)) { ok = false; break; }
+            TRACE(1, it);
             tc_fence_after_sync();
             const uint32_t sa = smem_u32(smem + stage * C::STAGE_BYTES);
             const uint64_t adesc = umma_desc_k_sw128(sa);
@@ -247,26 +261,47 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
       if (!mbar_wait(smem_u32(&aux->esync), eph, abort_flag)) ok = false;
       eph ^= 1u;
     };
+    // Scale products sc[kbl][j] = w_scale[e, m, kb] * b_scale[row0 + j, kb] of one item.  With two
+    // tables (small token tiles, short items) the next item's values are fetched into registers
+    // before the current item's K loop, so their global-memory latency is off the critical path.
+    constexpr int kEpiThreads = kEpiWarps * 32;
+    constexpr int kMaxE = (C::KB * N_TILE + kEpiThreads - 1) / kEpiThreads;
+    auto load_scale = [&](const Item& w, int idx) -> float {
+      const int nkb = w.kb1 - w.kb0;
+      if (idx >= nkb * N_TILE) return 0.0f;
+      const int kbl = idx / N_TILE, j = idx % N_TILE, kb = w.kb0 + kbl;
+      if (j >= w.valid) return 0.0f;
+      const float ws = __ldg(a.w_scale + (static_cast<size_t>(w.e) * C::MT + w.m) * C::KB + kb);
+      return ws * __ldg(a.b_scale + static_cast<size_t>(w.row0 + j) * C::KB + kb);
+    };
+    float pre[C::SC_BUFS == 2 ? kMaxE : 1];
+    if (C::SC_BUFS == 2 && static_cast<int>(blockIdx.x) < items) {
+      const Item w0 = decode_item<GEMM, N_TILE>(blockIdx.x, split, aux);
+#pragma unroll
+      for (int x = 0; x < kMaxE; ++x) {
+        const int idx = etid + x * kEpiThreads;
+        if (idx < C::KB * N_TILE) sc_base[idx] = load_scale(w0, idx);
+      }
+    }
     for (int i = blockIdx.x; ok && i < items; i += gridDim.x, ++nitem) {
       const Item w = decode_item<GEMM, N_TILE>(i, split, aux);
       const int nkb = w.kb1 - w.kb0;
+      if (etid == 0) TRACE(2, 128 + 2 * nitem);
       float* sc = sc_base + (C::SC_BUFS == 2 ? (nitem & 1u) * (C::KB * N_TILE) : 0);
+      const int inext = i + gridDim.x;
       if (C::SC_BUFS == 1) {
         epi_sync();   // the previous item's scale products are no longer being read
         if (!ok) break;
+        for (int idx = etid; idx < nkb * N_TILE; idx += kEpiThreads) sc[idx] = load_scale(w, idx);
       }
-      const float* ws = a.w_scale + (static_cast<size_t>(w.e) * C::MT + w.m) * C::KB;
-      for (int idx = etid; idx < nkb * N_TILE; idx += kEpiWarps * 32) {
-        const int kbl = idx / N_TILE, j = idx % N_TILE, kb = w.kb0 + kbl;
-        float bs = 0.0f;
-        if (j < w.valid) {
-          if (GEMM == 1) bs = __ldg(a.b_scale + static_cast<size_t>(kb) * a.T + __ldg(a.perm_token + w.row0 + j));
-          else bs = __ldg(a.b_scale + static_cast<size_t>(w.row0 + j) * kKB2 + kb);
-        }
-        sc[idx] = __ldg(ws + kb) * bs;
-      }
-      epi_sync();
+      epi_sync();     // this item's table is complete (and, with two tables, the other one is free)
       if (!ok) break;
+      if (C::SC_BUFS == 2 && inext < items) {
+        const Item wn = decode_item<GEMM, N_TILE>(inext, split, aux);
+#pragma unroll
+        for (int x = 0; x < kMaxE; ++x) pre[x] = load_scale(wn, etid + x * kEpiThreads);
+      }
+      if (etid == 0) TRACE(2, 128 + 2 * nitem + 1);
 
       float acc[C::CPW];
 #pragma unroll
@@ -276,6 +311,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
         const uint32_t buf = gi % C::NBUF, bph = (gi / C::NBUF) & 1u;
         const int gsize = min(C::G, nkb - kbl);
         if (!mbar_wait(smem_u32(&aux->tfull[buf]), bph, abort_flag)) { ok = false; break; }
+        if (etid == 0) TRACE(2, 8 + gi);
         tc_fence_after_sync();
         const uint32_t taddr = tmem_base + lane_addr + buf * (C::G * C::KB_COLS) + h * C::CPW;
         float v[C::G][C::PLANES][C::CPW];
@@ -317,11 +353,20 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
 #pragma unroll
       for (int j = 0; j < C::CPW; ++j)
         if (h * C::CPW + j < w.valid) out[static_cast<size_t>(j) * C::M_TOTAL] = acc[j];
+      if (C::SC_BUFS == 2 && inext < items) {
+        float* scn = sc_base + ((nitem + 1) & 1u) * (C::KB * N_TILE);
+#pragma unroll
+        for (int x = 0; x < kMaxE; ++x) {
+          const int idx = etid + x * kEpiThreads;
+          if (idx < C::KB * N_TILE) scn[idx] = pre[x];
+        }
+      }
     }
   }
 
   tc_fence_before_sync();
   __syncthreads();
+  if (threadIdx.x == 0) TRACE(3, 2);
   if (threadIdx.x == 0 && aux->abort) atomicOr(&sched->status, GEMM == 1 ? kErrGemm1Timeout : kErrGemm2Timeout);
   if (warp == 1) {
     __syncwarp();
@@ -333,8 +378,8 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
 template <int GEMM, int N_TILE>
 int launch_one(const CUtensorMap& tm_w, const CUtensorMap& tm_b, const GemmArgs& a, int ctas, cudaStream_t stream) {
   using C = Cfg<GEMM, N_TILE>;
-  grouped_gemm_kernel<GEMM, N_TILE><<<ctas, kThreads, C::SMEM_BYTES, stream>>>(tm_w, tm_b, a);
-  return static_cast<int>(cudaGetLastError());
+  return static_cast<int>(launch_pdl(grouped_gemm_kernel<GEMM, N_TILE>, dim3(ctas), dim3(kThreads), C::SMEM_BYTES,
+                                     stream, tm_w, tm_b, a));
 }
 
 template <int GEMM, int N_TILE>
@@ -345,6 +390,12 @@ int init_one() {
 }
 
 }  // namespace
+
+#ifdef MOE_TRACE
+extern "C" int moe_debug_trace(unsigned long long* host, int bytes) {
+  return static_cast<int>(cudaMemcpyFromSymbol(host, g_moe_trace, bytes));
+}
+#endif
 
 int grouped_gemm_init() {
   int rc = 0;

@@ -8,6 +8,34 @@
 
 namespace moe {
 
+// Programmatic dependent launch: every kernel of the operator is launched with the
+// programmatic-stream-serialization attribute, signals `launch_dependents` as its first
+// instruction (so the next kernel's launch latency, barrier initialisation and TMEM
+// allocation overlap this kernel's execution) and executes `griddep_wait` before its first
+// access to memory that an earlier kernel in the stream may still be writing.  Because the
+// signal is given at CTA start, the dependent grid can only be scheduled once every CTA of
+// this grid is resident, so early dependents never starve their prerequisite.
+#ifdef __CUDACC__
+__device__ __forceinline__ void griddep_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void griddep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                              Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+#endif
+
 struct RouteArgs {
   const float* logits;          // [T, 256]
   const uint16_t* bias_bf16;    // [256]
@@ -38,7 +66,10 @@ struct GatherArgs {
   const MoeSched* sched;
   const int* perm_token;
   const uint8_t* hidden;        // [T, 7168] e4m3
+  const float* hidden_scale;    // [56, T]
+  int T;
   uint8_t* a_packed;            // [rows_cap, 7168]
+  float* a_scale_rows;          // [rows_cap, 56] scales of each permuted row, row-major
 };
 
 // Grouped, swap-AB, split-K fp8 GEMM: out[slab][row, m] = sum_k W_e[m, k] * B[row, k] with the
@@ -47,9 +78,7 @@ struct GatherArgs {
 struct GemmArgs {
   MoeSched* sched;
   const float* w_scale;         // [32, M/128, K/128]
-  const float* b_scale;         // GEMM1: hidden_states_scale [56, T]; GEMM2: c_scale [rows, 16]
-  const int* perm_token;        // GEMM1: token of each row (to index b_scale); GEMM2: unused
-  int T;
+  const float* b_scale;         // per-row scales, row-major: GEMM1 [rows, 56]; GEMM2 [rows, 16]
   int b_plane_rows;             // GEMM2: rows between consecutive e4m3 planes of B (rows_cap); GEMM1: 0
   float* out;                   // fp32 slabs [split][n_sel_pad, M]
 };

@@ -190,6 +190,7 @@ extern "C" int moe_fp8_block_scale_layout(int T, moe_b200_layout* out) {
   out->perm_weight = L.perm_weight;
   out->tok_rows = L.tok_rows;
   out->a_packed = L.a_packed;
+  out->a_scale_rows = L.a_scale_rows;
   out->g1 = L.g1;
   out->cq = L.cq;
   out->c_scale = L.c_scale;
@@ -228,6 +229,7 @@ extern "C" int moe_fp8_block_scale_run(const float* routing_logits, const uint16
   float* perm_weight = reinterpret_cast<float*>(ws + L.perm_weight);
   int* tok_rows = reinterpret_cast<int*>(ws + L.tok_rows);
   uint8_t* a_packed = ws + L.a_packed;
+  float* a_scale_rows = reinterpret_cast<float*>(ws + L.a_scale_rows);
   float* g1 = reinterpret_cast<float*>(ws + L.g1);
   uint8_t* cq = ws + L.cq;
   float* c_scale = reinterpret_cast<float*>(ws + L.c_scale);
@@ -252,13 +254,13 @@ extern "C" int moe_fp8_block_scale_run(const float* routing_logits, const uint16
   g_launches += T <= 256 ? 1 : 2;
   stage_mark(1, stream);
 
-  GatherArgs ga{sched, perm_token, hidden_states, a_packed};
+  GatherArgs ga{sched, perm_token, hidden_states, hidden_states_scale, T, a_packed, a_scale_rows};
   launch_gather_rows(ga, T, stream);
   MOE_CUDA(cudaGetLastError());
   g_launches += 1;
   stage_mark(2, stream);
 
-  GemmArgs g1a{sched, gemm1_weights_scale, hidden_states_scale, perm_token, T, 0, g1};
+  GemmArgs g1a{sched, gemm1_weights_scale, a_scale_rows, 0, g1};
   if ((rc = launch_grouped_gemm(1, n_tile, tm_w13, tm_a, g1a, ctas, stream))) {
     g_last_cuda_error = rc;
     return MOE_B200_ECUDA;
@@ -272,7 +274,7 @@ extern "C" int moe_fp8_block_scale_run(const float* routing_logits, const uint16
   g_launches += 1;
   stage_mark(4, stream);
 
-  GemmArgs g2a{sched, gemm2_weights_scale, c_scale, nullptr, T, L.rows_cap, o};
+  GemmArgs g2a{sched, gemm2_weights_scale, c_scale, L.rows_cap, o};
   if ((rc = launch_grouped_gemm(2, n_tile, tm_w2, tm_c, g2a, ctas, stream))) {
     g_last_cuda_error = rc;
     return MOE_B200_ECUDA;

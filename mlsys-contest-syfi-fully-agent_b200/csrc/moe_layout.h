@@ -25,7 +25,7 @@ constexpr int kMT1 = k2I / kBlock;       // 32 weight-row tiles per expert in GE
 constexpr int kMT2 = kH / kBlock;        // 56 weight-row tiles per expert in GEMM2
 constexpr int kNTerms = 4;               // e4m3 terms the SwiGLU output is split into for GEMM2
 constexpr int kMaxSplit1 = 14;           // split-K limits (>= 4 K-blocks per split)
-constexpr int kMaxSplit2 = 4;
+constexpr int kMaxSplit2 = 8;
 constexpr int kMinSlabRows = 2048;       // slab capacity floor so that small batches can split K
 constexpr int kNumSMs = 148;
 
@@ -59,7 +59,7 @@ struct WorkspaceLayout {
   int rows_cap;        // capacity in rows: 8*T rounded up to 128
   int slab_rows;       // rows of the fp32 slab areas: max(rows_cap, kMinSlabRows)
   size_t sched, topk_idx, topk_w, local_mask, perm_token, perm_weight, tok_rows;
-  size_t a_packed, g1, cq, c_scale, o;
+  size_t a_packed, a_scale_rows, g1, cq, c_scale, o;
   size_t total;
 };
 
@@ -86,6 +86,7 @@ inline WorkspaceLayout make_layout(int T) {
   L.perm_weight = take(static_cast<size_t>(L.rows_cap) * 4);
   L.tok_rows = take(Tz * kTopK * 4);
   L.a_packed = take(static_cast<size_t>(L.rows_cap) * kH);
+  L.a_scale_rows = take(static_cast<size_t>(L.rows_cap) * kKB1 * 4);
   L.g1 = take(static_cast<size_t>(L.slab_rows) * k2I * 4);
   L.cq = take(static_cast<size_t>(kNTerms) * L.rows_cap * kI);
   L.c_scale = take(static_cast<size_t>(L.rows_cap) * kKB2 * 4);

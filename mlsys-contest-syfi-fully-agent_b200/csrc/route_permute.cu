@@ -208,17 +208,25 @@ __device__ void permute_block(const PermuteArgs& a) {
 // One warp per token, 8 warps per CTA.
 __global__ void __launch_bounds__(256) route_kernel(RouteArgs a) {
   __shared__ float bias_smem[kEGlobal];
+  griddep_launch_dependents();
+  griddep_wait();
   load_bias(a.bias_bf16, bias_smem);
   __syncthreads();
   const int warps = blockDim.x >> 5;
   route_tokens_strided(a, bias_smem, blockIdx.x * warps + (threadIdx.x >> 5), gridDim.x * warps, threadIdx.x & 31);
 }
 
-__global__ void __launch_bounds__(1024) permute_kernel(PermuteArgs a) { permute_block(a); }
+__global__ void __launch_bounds__(1024) permute_kernel(PermuteArgs a) {
+  griddep_launch_dependents();
+  griddep_wait();
+  permute_block(a);
+}
 
 // Small batches: routing and permutation in one single-CTA launch.
 __global__ void __launch_bounds__(1024) route_permute_kernel(RouteArgs r, PermuteArgs p) {
   __shared__ float bias_smem[kEGlobal];
+  griddep_launch_dependents();
+  griddep_wait();
   load_bias(r.bias_bf16, bias_smem);
   __syncthreads();
   route_tokens_strided(r, bias_smem, threadIdx.x >> 5, 32, threadIdx.x & 31);
@@ -228,36 +236,50 @@ __global__ void __launch_bounds__(1024) route_permute_kernel(RouteArgs r, Permut
 }
 
 // Packed copy of the fp8 activation rows in permuted order: a_packed[r, :] = hidden[perm_token[r], :]
-// (the B operand of GEMM1 is then one TMA box per token tile).  16 bytes per thread.
+// (the B operand of GEMM1 is then one TMA box per token tile), 16 bytes per thread, plus the
+// row's 56 block scales gathered from the transposed [56, T] layout into a row-major table.
 __global__ void __launch_bounds__(256) gather_rows_kernel(GatherArgs a) {
+  griddep_launch_dependents();
+  griddep_wait();
   const int n_sel = a.sched->n_sel;
-  constexpr int kChunks = kH / 16;   // 448 x 16 B per row
+  constexpr int kData = kH / 16;            // 448 x 16 B of fp8 per row
+  constexpr int kChunks = kData + kKB1 / 4; // + 14 x 4 scales
   const long long total = static_cast<long long>(n_sel) * kChunks;
   for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
        i += static_cast<long long>(gridDim.x) * blockDim.x) {
     const int r = static_cast<int>(i / kChunks), c = static_cast<int>(i % kChunks);
     const int t = a.perm_token[r];
-    reinterpret_cast<uint4*>(a.a_packed + static_cast<size_t>(r) * kH)[c] =
-        __ldg(reinterpret_cast<const uint4*>(a.hidden + static_cast<size_t>(t) * kH) + c);
+    if (c < kData) {
+      reinterpret_cast<uint4*>(a.a_packed + static_cast<size_t>(r) * kH)[c] =
+          __ldg(reinterpret_cast<const uint4*>(a.hidden + static_cast<size_t>(t) * kH) + c);
+    } else {
+      const int kb = (c - kData) * 4;
+      float4 v;
+      v.x = __ldg(a.hidden_scale + static_cast<size_t>(kb + 0) * a.T + t);
+      v.y = __ldg(a.hidden_scale + static_cast<size_t>(kb + 1) * a.T + t);
+      v.z = __ldg(a.hidden_scale + static_cast<size_t>(kb + 2) * a.T + t);
+      v.w = __ldg(a.hidden_scale + static_cast<size_t>(kb + 3) * a.T + t);
+      reinterpret_cast<float4*>(a.a_scale_rows + static_cast<size_t>(r) * kKB1)[c - kData] = v;
+    }
   }
 }
 
 void launch_route_permute(const RouteArgs& r, const PermuteArgs& p, cudaStream_t stream) {
   if (r.T <= 256) {
-    route_permute_kernel<<<1, 1024, 0, stream>>>(r, p);
+    launch_pdl(route_permute_kernel, dim3(1), dim3(1024), 0, stream, r, p);
   } else {
     const int grid = (r.T + 7) / 8 < 4 * kNumSMs ? (r.T + 7) / 8 : 4 * kNumSMs;
-    route_kernel<<<grid, 256, 0, stream>>>(r);
-    permute_kernel<<<1, 1024, 0, stream>>>(p);
+    launch_pdl(route_kernel, dim3(grid), dim3(256), 0, stream, r);
+    launch_pdl(permute_kernel, dim3(1), dim3(1024), 0, stream, p);
   }
 }
 
 void launch_gather_rows(const GatherArgs& a, int T, cudaStream_t stream) {
-  long long chunks = static_cast<long long>(T) * kTopK * (kH / 16);
+  long long chunks = static_cast<long long>(T) * kTopK * (kH / 16 + kKB1 / 4);
   long long blocks = (chunks + 255) / 256;
   if (blocks > 8 * kNumSMs) blocks = 8 * kNumSMs;
   if (blocks < 1) blocks = 1;
-  gather_rows_kernel<<<static_cast<int>(blocks), 256, 0, stream>>>(a);
+  launch_pdl(gather_rows_kernel, dim3(static_cast<unsigned>(blocks)), dim3(256), 0, stream, a);
 }
 
 }  // namespace moe

@@ -33,6 +33,8 @@ __device__ __forceinline__ float from_e4m3(uint8_t b) {
 
 // One warp per (row, 128-column block); lane owns 4 consecutive columns.
 __global__ void __launch_bounds__(256) swiglu_split_kernel(SwigluArgs a) {
+  griddep_launch_dependents();
+  griddep_wait();
   const MoeSched* sc = a.sched;
   const int n_sel = sc->n_sel, split = sc->split1;
   const size_t slab = static_cast<size_t>(sc->n_sel_pad) * k2I;
@@ -94,6 +96,8 @@ __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
 
 // One thread per 4 output columns of a token.
 __global__ void __launch_bounds__(256) combine_kernel(CombineArgs a) {
+  griddep_launch_dependents();
+  griddep_wait();
   const MoeSched* sc = a.sched;
   const int split = sc->split2;
   const size_t slab = static_cast<size_t>(sc->n_sel_pad) * kH;
@@ -133,7 +137,7 @@ void launch_swiglu_split(const SwigluArgs& a, int T, cudaStream_t stream) {
   long long blocks = (warps + 7) / 8;
   if (blocks > 8 * kNumSMs) blocks = 8 * kNumSMs;
   if (blocks < 1) blocks = 1;
-  swiglu_split_kernel<<<static_cast<int>(blocks), 256, 0, stream>>>(a);
+  launch_pdl(swiglu_split_kernel, dim3(static_cast<unsigned>(blocks)), dim3(256), 0, stream, a);
 }
 
 void launch_combine(const CombineArgs& a, cudaStream_t stream) {
@@ -141,7 +145,7 @@ void launch_combine(const CombineArgs& a, cudaStream_t stream) {
   long long blocks = (threads + 255) / 256;
   if (blocks > 8 * kNumSMs) blocks = 8 * kNumSMs;
   if (blocks < 1) blocks = 1;
-  combine_kernel<<<static_cast<int>(blocks), 256, 0, stream>>>(a);
+  launch_pdl(combine_kernel, dim3(static_cast<unsigned>(blocks)), dim3(256), 0, stream, a);
 }
 
 }  // namespace moe

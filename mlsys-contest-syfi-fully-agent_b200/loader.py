@@ -10,7 +10,7 @@ import ctypes
 import os
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(HERE, "libmoe_b200.so")
+LIB_PATH = os.environ.get("MOE_B200_LIB") or os.path.join(HERE, "libmoe_b200.so")   # override: debug builds
 
 OK, EINVAL, EWORKSPACE, ECUDA, EDEVICE, EKERNEL = 0, -1, -2, -3, -4, -5
 ERROR_NAMES = {OK: "ok", EINVAL: "invalid argument", EWORKSPACE: "workspace too small", ECUDA: "CUDA error",
@@ -34,7 +34,7 @@ class Layout(ctypes.Structure):
     _fields_ = [("T", ctypes.c_int32), ("rows_cap", ctypes.c_int32), ("slab_rows", ctypes.c_int32),
                 ("n_terms", ctypes.c_int32)] + \
                [(n, ctypes.c_uint64) for n in ("sched", "topk_idx", "topk_w", "local_mask", "perm_token",
-                                               "perm_weight", "tok_rows", "a_packed", "g1", "cq", "c_scale", "o",
+                                               "perm_weight", "tok_rows", "a_packed", "a_scale_rows", "g1", "cq", "c_scale", "o",
                                                "total")]
 
 

@@ -40,7 +40,7 @@ def test_workspace_size_and_layout(loader):
         L = loader.layout(T)
         assert L.total == n and L.rows_cap >= 8 * T and L.rows_cap % 128 == 0
         offs = [L.sched, L.topk_idx, L.topk_w, L.local_mask, L.perm_token, L.perm_weight, L.tok_rows,
-                L.a_packed, L.g1, L.cq, L.c_scale, L.o]
+                L.a_packed, L.a_scale_rows, L.g1, L.cq, L.c_scale, L.o]
         assert offs == sorted(offs) and all(o % 1024 == 0 for o in offs) and offs[-1] < n
     assert loader.workspace_bytes(-1) == 0
     assert ctypes.sizeof(loader.Sched) == (16 + 32 + 33 + 33) * 4
