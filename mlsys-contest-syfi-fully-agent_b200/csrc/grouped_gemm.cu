@@ -72,7 +72,10 @@ struct Cfg {
   static constexpr int CPW = N_TILE / 2;                                // token columns per epilogue warp
   static constexpr int A_BYTES = 128 * 128;
   static constexpr int B_BYTES = N_TILE * 128;
-  static constexpr int STAGE_BYTES = A_BYTES + NTERMS * B_BYTES;
+  static constexpr int KB_BYTES = A_BYTES + NTERMS * B_BYTES;           // operands of one K-block
+  static constexpr int KPS = KB_BYTES <= 24 * 1024 ? 2 : 1;             // K-blocks per pipeline stage (one TMA each
+                                                                        // for the weights and the tokens per stage)
+  static constexpr int STAGE_BYTES = KPS * KB_BYTES;
   static constexpr int SC_BUFS = N_TILE <= 32 ? 2 : 1;                  // scale-product tables
   static constexpr int SC_BYTES = SC_BUFS * KB * N_TILE * 4;
   static constexpr int AUX_BYTES = 1024;
@@ -81,6 +84,7 @@ struct Cfg {
   static constexpr int STAGES = STAGES_FIT > 10 ? 10 : STAGES_FIT;
   static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + SC_BYTES + AUX_BYTES + 1024;
   static_assert(STAGES >= 2, "ring too small");
+  static_assert(KB % KPS == 0, "K-blocks per stage must divide the K extent");
   static_assert(NBUF >= 2 && TMEM_USED <= 512, "TMEM budget");
   static_assert(N_MMA % 16 == 0 && N_MMA >= 16 && N_MMA <= 256, "invalid UMMA N for M = 128");
   static_assert(SMEM_BYTES > 116 * 1024, "one CTA per SM is assumed (TMEM is allocated without contention)");
@@ -124,8 +128,10 @@ __device__ __forceinline__ Item decode_item(int i, int split, const Aux* aux) {
   const int cnt = aux->offs[e + 1] - aux->offs[e];
   it.row0 = aux->offs[e] + n * N_TILE;
   it.valid = min(N_TILE, cnt - n * N_TILE);
-  it.kb0 = (it.s * C::KB) / split;
-  it.kb1 = ((it.s + 1) * C::KB) / split;
+  // split boundaries in units of one pipeline stage, so that no stage straddles two items
+  constexpr int kUnits = C::KB / C::KPS;
+  it.kb0 = ((it.s * kUnits) / split) * C::KPS;
+  it.kb1 = (((it.s + 1) * kUnits) / split) * C::KPS;
   return it;
 }
 
@@ -199,17 +205,17 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
       for (int i = blockIdx.x; ok && i < items; i += gridDim.x) {
         const Item w = decode_item<GEMM, N_TILE>(i, split, aux);
         const int wy = w.e * C::M_TOTAL + w.m * 128;
-        for (int kb = w.kb0; kb < w.kb1; ++kb, ++it) {
+        for (int kb = w.kb0; kb < w.kb1; kb += C::KPS, ++it) {
           const uint32_t stage = it % C::STAGES, ph = (it / C::STAGES) & 1u;
           if (!mbar_wait(smem_u32(&aux->empty[stage]), ph ^ 1u, abort_flag)) { ok = false; break; }
           TRACE(0, it);
           const uint32_t bar = smem_u32(&aux->full[stage]);
           mbar_arrive_expect_tx(bar, C::STAGE_BYTES);
           const uint32_t dst = smem_u32(smem + stage * C::STAGE_BYTES);
-          tma_load_2d(dst, &tm_w, kb * 128, wy, bar);
-#pragma unroll
-          for (int t = 0; t < C::NTERMS; ++t)
-            tma_load_2d(dst + C::A_BYTES + t * C::B_BYTES, &tm_b, kb * 128, t * a.b_plane_rows + w.row0, bar);
+          // weights: [KPS][128 rows][128 B]; tokens: [KPS][NTERMS planes][N_TILE rows][128 B]
+          tma_load_3d(dst, &tm_w, 0, wy, kb, bar);
+          if (GEMM == 1) tma_load_3d(dst + C::KPS * C::A_BYTES, &tm_b, 0, w.row0, kb, bar);
+          else tma_load_4d(dst + C::KPS * C::A_BYTES, &tm_b, 0, w.row0, 0, kb, bar);
         }
       }
     }
@@ -226,22 +232,29 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
           const uint32_t buf = gi % C::NBUF, bph = (gi / C::NBUF) & 1u;
           if (!mbar_wait(smem_u32(&aux->tempty[buf]), bph ^ 1u, abort_flag)) { ok = false; break; }
           const int gsize = min(C::G, nkb - kbl);
-          for (int g = 0; g < gsize; ++g, ++it) {
+          for (int g = 0; g < gsize; ++g) {
+            const int u = (kbl + g) % C::KPS;          // K-block inside the current stage
             const uint32_t stage = it % C::STAGES, ph = (it / C::STAGES) & 1u;
-            if (!mbar_wait(smem_u32(&aux->full[stage]), ph, abort_flag)) { ok = false; break; }
-            TRACE(1, it);
-            tc_fence_after_sync();
-            const uint32_t sa = smem_u32(smem + stage * C::STAGE_BYTES);
-            const uint64_t adesc = umma_desc_k_sw128(sa);
+            if (u == 0) {
+              if (!mbar_wait(smem_u32(&aux->full[stage]), ph, abort_flag)) { ok = false; break; }
+              TRACE(1, it);
+              tc_fence_after_sync();
+            }
+            const uint32_t sbase = smem_u32(smem + stage * C::STAGE_BYTES);
+            const uint64_t adesc = umma_desc_k_sw128(sbase + u * C::A_BYTES);
+            const uint32_t sb = sbase + C::KPS * C::A_BYTES + u * (C::NTERMS * C::B_BYTES);
             const uint32_t d = tmem_base + buf * (C::G * C::KB_COLS) + g * C::KB_COLS;
 #pragma unroll
             for (int t = 0; t < C::MMA_PER_K4; ++t) {
-              const uint64_t bdesc = umma_desc_k_sw128(sa + C::A_BYTES + t * C::B_BYTES);
+              const uint64_t bdesc = umma_desc_k_sw128(sb + t * C::B_BYTES);
 #pragma unroll
               for (int k4 = 0; k4 < 4; ++k4)   // +32 bytes of K inside the 128-byte swizzle atom = +2 encoded units
                 umma_f8(d, adesc + 2 * k4, bdesc + 2 * k4, idesc, (t | k4) != 0 ? 1u : 0u);
             }
-            umma_commit(smem_u32(&aux->empty[stage]));
+            if (u == C::KPS - 1) {               // items span whole stages, so this is also the item's last K-block
+              umma_commit(smem_u32(&aux->empty[stage]));
+              ++it;
+            }
           }
           if (ok) umma_commit(smem_u32(&aux->tfull[buf]));
         }
@@ -396,6 +409,15 @@ extern "C" int moe_debug_trace(unsigned long long* host, int bytes) {
   return static_cast<int>(cudaMemcpyFromSymbol(host, g_moe_trace, bytes));
 }
 #endif
+
+int grouped_gemm_kblocks_per_stage(int gemm_id, int n_tile) {
+#define MOE_CASE(G, N) \
+  if (gemm_id == G && n_tile == N) return Cfg<G, N>::KPS;
+  MOE_CASE(1, 16) MOE_CASE(1, 32) MOE_CASE(1, 64) MOE_CASE(1, 128)
+  MOE_CASE(2, 16) MOE_CASE(2, 32) MOE_CASE(2, 64) MOE_CASE(2, 128)
+#undef MOE_CASE
+  return 1;
+}
 
 int grouped_gemm_init() {
   int rc = 0;

@@ -79,7 +79,6 @@ struct GemmArgs {
   MoeSched* sched;
   const float* w_scale;         // [32, M/128, K/128]
   const float* b_scale;         // per-row scales, row-major: GEMM1 [rows, 56]; GEMM2 [rows, 16]
-  int b_plane_rows;             // GEMM2: rows between consecutive e4m3 planes of B (rows_cap); GEMM1: 0
   float* out;                   // fp32 slabs [split][n_sel_pad, M]
 };
 
@@ -106,6 +105,7 @@ void launch_gather_rows(const GatherArgs& a, int T, cudaStream_t stream);
 // gemm_id 1 or 2; n_tile in {16, 32, 64, 128}.  Returns a cudaError_t as int.
 int launch_grouped_gemm(int gemm_id, int n_tile, const CUtensorMap& tm_w, const CUtensorMap& tm_b, const GemmArgs& a,
                         int ctas, cudaStream_t stream);
+int grouped_gemm_kblocks_per_stage(int gemm_id, int n_tile);   // K-blocks one TMA box of that kernel brings
 int grouped_gemm_init();   // one-time function attributes (dynamic shared memory opt-in)
 void launch_swiglu_split(const SwigluArgs& a, int T, cudaStream_t stream);
 void launch_combine(const CombineArgs& a, cudaStream_t stream);

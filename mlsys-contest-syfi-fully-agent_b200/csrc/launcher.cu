@@ -84,8 +84,18 @@ DeviceState g_dev[16];
 
 struct MapKey {
   const void* ptr;
-  uint64_t rows, cols;
-  uint32_t box_rows;
+  uint32_t rank;
+  uint64_t dims[4];
+  uint64_t strides[3];
+  uint32_t box[4];
+  bool operator==(const MapKey& o) const {
+    if (ptr != o.ptr || rank != o.rank) return false;
+    for (uint32_t i = 0; i < rank; ++i)
+      if (dims[i] != o.dims[i] || box[i] != o.box[i]) return false;
+    for (uint32_t i = 0; i + 1 < rank; ++i)
+      if (strides[i] != o.strides[i]) return false;
+    return true;
+  }
 };
 struct MapEntry {
   MapKey key;
@@ -121,33 +131,57 @@ int ensure_device(DeviceState** out) {
   return MOE_B200_OK;
 }
 
-// 2-D u8 tensor [rows, cols] row-major, box [box_rows, 128 bytes], 128-byte swizzle.
-int get_map(DeviceState* d, const void* ptr, uint64_t rows, uint64_t cols, uint32_t box_rows, CUtensorMap* out) {
+// u8 tensor map with the 128-byte swizzle; dims / box innermost first, strides in bytes for dims 1..rank-1.
+int get_map(DeviceState* d, const MapKey& key, CUtensorMap* out) {
   std::lock_guard<std::mutex> lk(g_mu);
   for (auto& e : g_maps)
-    if (e.used && e.key.ptr == ptr && e.key.rows == rows && e.key.cols == cols && e.key.box_rows == box_rows) {
+    if (e.used && e.key == key) {
       *out = e.map;
       return MOE_B200_OK;
     }
-  cuuint64_t dims[2] = {cols, rows};
-  cuuint64_t strides[1] = {cols};
-  cuuint32_t box[2] = {128, box_rows};
-  cuuint32_t estr[2] = {1, 1};
+  cuuint64_t dims[4], strides[3];
+  cuuint32_t box[4], estr[4] = {1, 1, 1, 1};
+  for (uint32_t i = 0; i < key.rank; ++i) { dims[i] = key.dims[i]; box[i] = key.box[i]; }
+  for (uint32_t i = 0; i + 1 < key.rank; ++i) strides[i] = key.strides[i];
   CUtensorMap m;
-  CUresult r = d->encode(&m, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(ptr), dims, strides, box, estr,
-                         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  CUresult r = d->encode(&m, CU_TENSOR_MAP_DATA_TYPE_UINT8, key.rank, const_cast<void*>(key.ptr), dims, strides, box,
+                         estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                         CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) {
     g_last_cuda_error = 100000 + static_cast<int>(r);
     return MOE_B200_ECUDA;
   }
   MapEntry& e = g_maps[g_map_next];
   g_map_next = (g_map_next + 1) % 32;
-  e.key = MapKey{ptr, rows, cols, box_rows};
+  e.key = key;
   e.map = m;
   e.used = true;
   *out = m;
   return MOE_B200_OK;
+}
+
+// Operand [rows, K] (row-major, K in bytes) seen as [128 B inside a K-block, rows, K / 128 K-blocks]:
+// one box brings `kps` consecutive K-blocks of `box_rows` rows as `kps` swizzled [box_rows x 128 B] tiles.
+MapKey kblock_map(const void* ptr, uint64_t rows, uint64_t K, uint32_t box_rows, uint32_t kps) {
+  MapKey k{};
+  k.ptr = ptr;
+  k.rank = 3;
+  k.dims[0] = 128; k.dims[1] = rows; k.dims[2] = K / 128;
+  k.strides[0] = K; k.strides[1] = 128;
+  k.box[0] = 128; k.box[1] = box_rows; k.box[2] = kps;
+  return k;
+}
+
+// The kNTerms e4m3 planes [plane][rows, 2048] of GEMM2's token operand as
+// [128 B, rows, planes, K-blocks]: one box brings all planes of `kps` K-blocks, plane-major inside a K-block.
+MapKey planes_map(const void* ptr, uint64_t rows, uint32_t box_rows, uint32_t kps) {
+  MapKey k{};
+  k.ptr = ptr;
+  k.rank = 4;
+  k.dims[0] = 128; k.dims[1] = rows; k.dims[2] = kNTerms; k.dims[3] = kI / 128;
+  k.strides[0] = kI; k.strides[1] = rows * kI; k.strides[2] = 128;
+  k.box[0] = 128; k.box[1] = box_rows; k.box[2] = kNTerms; k.box[3] = kps;
+  return k;
 }
 
 int pick_n_tile(int T) {
@@ -239,10 +273,13 @@ extern "C" int moe_fp8_block_scale_run(const float* routing_logits, const uint16
   const int ctas = dev->sm_count;
 
   CUtensorMap tm_w13, tm_w2, tm_a, tm_c;
-  if ((rc = get_map(dev, gemm1_weights, static_cast<uint64_t>(kELocal) * k2I, kH, 128, &tm_w13))) return rc;
-  if ((rc = get_map(dev, gemm2_weights, static_cast<uint64_t>(kELocal) * kH, kI, 128, &tm_w2))) return rc;
-  if ((rc = get_map(dev, a_packed, L.rows_cap, kH, n_tile, &tm_a))) return rc;
-  if ((rc = get_map(dev, cq, static_cast<uint64_t>(kNTerms) * L.rows_cap, kI, n_tile, &tm_c))) return rc;
+  const uint32_t kps1 = grouped_gemm_kblocks_per_stage(1, n_tile), kps2 = grouped_gemm_kblocks_per_stage(2, n_tile);
+  if ((rc = get_map(dev, kblock_map(gemm1_weights, static_cast<uint64_t>(kELocal) * k2I, kH, 128, kps1), &tm_w13)))
+    return rc;
+  if ((rc = get_map(dev, kblock_map(gemm2_weights, static_cast<uint64_t>(kELocal) * kH, kI, 128, kps2), &tm_w2)))
+    return rc;
+  if ((rc = get_map(dev, kblock_map(a_packed, L.rows_cap, kH, n_tile, kps1), &tm_a))) return rc;
+  if ((rc = get_map(dev, planes_map(cq, L.rows_cap, n_tile, kps2), &tm_c))) return rc;
 
   RouteArgs ra{routing_logits, routing_bias, T, local_expert_offset, routed_scaling_factor, topk_idx, topk_w,
                local_mask};
@@ -260,7 +297,7 @@ extern "C" int moe_fp8_block_scale_run(const float* routing_logits, const uint16
   g_launches += 1;
   stage_mark(2, stream);
 
-  GemmArgs g1a{sched, gemm1_weights_scale, a_scale_rows, 0, g1};
+  GemmArgs g1a{sched, gemm1_weights_scale, a_scale_rows, g1};
   if ((rc = launch_grouped_gemm(1, n_tile, tm_w13, tm_a, g1a, ctas, stream))) {
     g_last_cuda_error = rc;
     return MOE_B200_ECUDA;
@@ -274,7 +311,7 @@ extern "C" int moe_fp8_block_scale_run(const float* routing_logits, const uint16
   g_launches += 1;
   stage_mark(4, stream);
 
-  GemmArgs g2a{sched, gemm2_weights_scale, c_scale, L.rows_cap, o};
+  GemmArgs g2a{sched, gemm2_weights_scale, c_scale, o};
   if ((rc = launch_grouped_gemm(2, n_tile, tm_w2, tm_c, g2a, ctas, stream))) {
     g_last_cuda_error = rc;
     return MOE_B200_ECUDA;
