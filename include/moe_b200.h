@@ -115,6 +115,25 @@ long long moe_fp8_block_scale_launch_count(void);
 int moe_fp8_block_scale_set_profiling(int enable);
 int moe_fp8_block_scale_stage_times(float* ms, int n);
 
+/* No counterpart in the reference.  The routing / histogram / prefix-sum /
+ * permutation stage for callers that cannot allocate device memory when they need
+ * it (a plugin inside an engine that owns all memory, or code that runs while the
+ * allocator is off limits): the stage's scratch lives in a fixed ~150 KB device
+ * array inside the library instead of a caller workspace.
+ *   in : routing_logits f32 [T, 256], routing_bias bf16 [256]
+ *   out: topk_idx i32 [T, 8], topk_w f32 [T, 8], expert_offsets i32 [33] (exclusive
+ *        prefix of tokens per local expert), perm_token i32 [8 T] and perm_weight
+ *        f32 [8 T] (first expert_offsets[32] entries valid: ascending token inside
+ *        ascending local expert)
+ * T above MOE_B200_STATIC_MAX_TOKENS returns MOE_B200_EINVAL.  The first call on a
+ * device resolves the array's address and should come before any stream capture.
+ * All calls on a device share the array, so calls that overlap on the GPU race. */
+#define MOE_B200_STATIC_MAX_TOKENS 4096
+int moe_fp8_block_scale_route_static(const float* routing_logits, const uint16_t* routing_bias, int T,
+                                     int local_expert_offset, float routed_scaling_factor,
+                                     int32_t* topk_idx, float* topk_w, int32_t* expert_offsets,
+                                     int32_t* perm_token, float* perm_weight, void* stream);
+
 #ifdef __cplusplus
 }
 #endif
