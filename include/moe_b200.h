@@ -63,6 +63,17 @@ int moe_fp8_block_scale_run_host(const float* routing_logits_host, const uint16_
                                  int T, int local_expert_offset, float routed_scaling_factor,
                                  uint16_t* output_host, void* workspace, size_t workspace_bytes, void* stream);
 
+/* Routing alone (the first stage of the operator): the eight selected global
+ * experts per token in descending biased-score order, their combination weights,
+ * and a bit mask of the experts that fall in [local_expert_offset,
+ * local_expert_offset + 32).  Same arithmetic as the operator's own routing
+ * (reference route_kernel, moe/solution/cuda/moe.cu:60-186; definition
+ * references/moe.py:123-158).  The expert-parallel layer uses it to decide where
+ * each token is dispatched.  topk_idx i32 [T,8], topk_w f32 [T,8], local_mask u32 [T]. */
+int moe_fp8_block_scale_route(const float* routing_logits, const uint16_t* routing_bias, int T,
+                              int local_expert_offset, float routed_scaling_factor,
+                              int32_t* topk_idx, float* topk_w, uint32_t* local_mask, void* stream);
+
 /* Waits for `stream` and returns the error bits the kernels of the last call on
  * this workspace recorded (0 = none) in *status.  The reference checks no CUDA
  * return code at all (moe.cu:2729-2894); this is the replacement's error channel. */

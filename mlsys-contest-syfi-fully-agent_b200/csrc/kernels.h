@@ -101,6 +101,7 @@ struct CombineArgs {
 };
 
 void launch_route_permute(const RouteArgs& r, const PermuteArgs& p, cudaStream_t stream);
+void launch_route_only(const RouteArgs& r, cudaStream_t stream);
 void launch_gather_rows(const GatherArgs& a, int T, cudaStream_t stream);
 // gemm_id 1 or 2; n_tile in {16, 32, 64, 128}.  Returns a cudaError_t as int.
 int launch_grouped_gemm(int gemm_id, int n_tile, const CUtensorMap& tm_w, const CUtensorMap& tm_b, const GemmArgs& a,

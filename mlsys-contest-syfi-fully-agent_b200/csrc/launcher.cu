@@ -362,6 +362,20 @@ extern "C" int moe_fp8_block_scale_run_host(const float* routing_logits_host, co
   return MOE_B200_OK;
 }
 
+extern "C" int moe_fp8_block_scale_route(const float* routing_logits, const uint16_t* routing_bias, int T,
+                                         int local_expert_offset, float routed_scaling_factor, int32_t* topk_idx,
+                                         float* topk_w, uint32_t* local_mask, void* stream_v) {
+  if (T < 0) return MOE_B200_EINVAL;
+  if (T == 0) return MOE_B200_OK;
+  if (!routing_logits || !routing_bias || !topk_idx || !topk_w || !local_mask) return MOE_B200_EINVAL;
+  RouteArgs ra{routing_logits, routing_bias, T, local_expert_offset, routed_scaling_factor, topk_idx, topk_w,
+               local_mask};
+  launch_route_only(ra, static_cast<cudaStream_t>(stream_v));
+  MOE_CUDA(cudaGetLastError());
+  g_launches += 1;
+  return MOE_B200_OK;
+}
+
 extern "C" int moe_fp8_block_scale_status(const void* workspace, void* stream_v, int* status) {
   if (!workspace || !status) return MOE_B200_EINVAL;
   cudaStream_t stream = static_cast<cudaStream_t>(stream_v);

@@ -274,6 +274,11 @@ void launch_route_permute(const RouteArgs& r, const PermuteArgs& p, cudaStream_t
   }
 }
 
+void launch_route_only(const RouteArgs& r, cudaStream_t stream) {
+  const int grid = (r.T + 7) / 8 < 4 * kNumSMs ? (r.T + 7) / 8 : 4 * kNumSMs;
+  launch_pdl(route_kernel, dim3(grid), dim3(256), 0, stream, r);
+}
+
 void launch_gather_rows(const GatherArgs& a, int T, cudaStream_t stream) {
   long long chunks = static_cast<long long>(T) * kTopK * (kH / 16 + kKB1 / 4);
   long long blocks = (chunks + 255) / 256;

@@ -143,6 +143,23 @@ def run_host(routing_logits, routing_bias, hidden_states, hidden_states_scale, g
     return output
 
 
+def route(routing_logits: torch.Tensor, routing_bias: torch.Tensor, local_expert_offset: int,
+          routed_scaling_factor: float):
+    """Routing alone: (topk_idx i32 [T,8], topk_w f32 [T,8], local_mask i32 [T]) on the current stream."""
+    T = routing_logits.shape[0]
+    dev = routing_logits.device
+    idx = torch.empty((T, 8), dtype=torch.int32, device=dev)
+    w = torch.empty((T, 8), dtype=torch.float32, device=dev)
+    mask = torch.empty((T,), dtype=torch.int32, device=dev)
+    if T:
+        with torch.cuda.device(dev):
+            loader.check(loader.lib.moe_fp8_block_scale_route(
+                routing_logits.data_ptr(), routing_bias.data_ptr(), int(T), int(local_expert_offset),
+                float(routed_scaling_factor), idx.data_ptr(), w.data_ptr(), mask.data_ptr(),
+                torch.cuda.current_stream(dev).cuda_stream))
+    return idx, w, mask
+
+
 def kernel_status(workspace: Optional[Workspace] = None, device=None) -> int:
     """Waits for the current stream and returns the kernels' error bits (0 = none)."""
     dev = torch.device(device if device is not None else "cuda")
