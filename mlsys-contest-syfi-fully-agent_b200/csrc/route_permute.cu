@@ -128,25 +128,59 @@ __device__ int choose_split(int tiles, int max_split, int ctas, int n_sel_pad, i
   return best;
 }
 
-// Block-wide (1024 threads, warp w <-> local expert w) histogram, scan, stable permutation
-// and schedule.  Requires the routing outputs of all T tokens to be visible.
+// Best split-K factors, evaluated one candidate per lane.
+__device__ int choose_split_warp(int tiles, int max_split, int ctas, int n_sel_pad, int slab_rows, int lane) {
+  if (tiles <= 0) return 1;
+  const int S = lane + 1;
+  float eff = 0.0f;
+  if (S <= max_split && static_cast<long long>(S) * n_sel_pad <= slab_rows) {
+    const int items = tiles * S;
+    const int waves = (items + ctas - 1) / ctas;
+    eff = static_cast<float>(items) / static_cast<float>(waves * ctas);
+  }
+  // same rule as choose_split: walk S upwards, move on only for a > 4 % fuller last wave
+  int best = 1;
+  float best_eff = 0.0f;
+  for (int k = 0; k < max_split; ++k) {
+    const float e = __shfl_sync(0xFFFFFFFFu, eff, k);
+    if (e > best_eff * 1.04f) { best_eff = e; best = k + 1; }
+  }
+  return best;
+}
+
+// Block-wide (1024 threads) histogram, scan, stable permutation and schedule.  Warp w owns
+// the contiguous token range [w * span, (w + 1) * span); inside a 32-token chunk lane = token.
+// Phase 1 counts, per warp and expert, the tokens that selected the expert; an exclusive
+// scan over (expert, warp) then gives every warp its first row for every expert, and phase
+// 2 fills rows in token order, so rows are ascending in token inside ascending expert.
+// Requires the routing outputs of all T tokens to be visible.
 __device__ void permute_block(const PermuteArgs& a) {
-  __shared__ int s_counts[kELocal];
+  __shared__ int s_wcount[32][kELocal + 1];     // [warp][expert]: count, then first row (+1: no bank conflicts)
   __shared__ int s_offs[kELocal + 1];
   const int lane = threadIdx.x & 31;
-  const int le = threadIdx.x >> 5;
+  const int warp = threadIdx.x >> 5;
   const uint32_t lt_mask = (1u << lane) - 1u;
+  const int chunks = (a.T + 31) / 32;
+  const int span = (chunks + 31) / 32;          // chunks per warp
+  const int c0 = warp * span, c1 = min(chunks, c0 + span);
 
-  int count = 0;
-  for (int t0 = 0; t0 < a.T; t0 += 32) {
-    const int t = t0 + lane;
+  // phase 1: lane le accumulates this warp's count for expert le
+  int cnt = 0;
+  for (int c = c0; c < c1; ++c) {
+    const int t = c * 32 + lane;
     const uint32_t m = t < a.T ? a.local_mask[t] : 0u;
-    count += __popc(__ballot_sync(0xFFFFFFFFu, (m >> le) & 1u));
+#pragma unroll
+    for (int le = 0; le < kELocal; ++le) {
+      const int n = __popc(__ballot_sync(0xFFFFFFFFu, (m >> le) & 1u));
+      if (lane == le) cnt += n;
+    }
   }
-  if (lane == 0) s_counts[le] = count;
+  s_wcount[warp][lane] = cnt;
   __syncthreads();
-  if (threadIdx.x < 32) {
-    const int c = s_counts[lane];
+  if (warp == 0) {
+    // lane = expert: totals over warps, exclusive scan over experts, per-warp first rows
+    int c = 0;
+    for (int w = 0; w < 32; ++w) c += s_wcount[w][lane];
     const int tiles = (c + a.n_tile - 1) / a.n_tile;
     int inc = c, tinc = tiles;
 #pragma unroll
@@ -155,20 +189,26 @@ __device__ void permute_block(const PermuteArgs& a) {
       const int tv = __shfl_up_sync(0xFFFFFFFFu, tinc, d);
       if (lane >= d) { inc += v; tinc += tv; }
     }
+    int run = inc - c;                          // first row of expert `lane`
+    for (int w = 0; w < 32; ++w) {
+      const int n = s_wcount[w][lane];
+      s_wcount[w][lane] = run;
+      run += n;
+    }
     MoeSched* sc = a.sched;
     s_offs[lane + 1] = inc;
     sc->counts[lane] = c;
     sc->offs[lane + 1] = inc;
     sc->tile_prefix[lane + 1] = tinc;
     const uint32_t act = __ballot_sync(0xFFFFFFFFu, c > 0);
+    const int n_sel = __shfl_sync(0xFFFFFFFFu, inc, 31), tiles_total = __shfl_sync(0xFFFFFFFFu, tinc, 31);
+    const int n_sel_pad = (n_sel + 15) & ~15;
+    const int s1 = choose_split_warp(tiles_total * kMT1, kMaxSplit1, a.ctas, n_sel_pad, a.slab_rows, lane);
+    const int s2 = choose_split_warp(tiles_total * kMT2, kMaxSplit2, a.ctas, n_sel_pad, a.slab_rows, lane);
     if (lane == 31) {
       s_offs[0] = 0;
       sc->offs[0] = 0;
       sc->tile_prefix[0] = 0;
-      const int n_sel = inc, tiles_total = tinc;
-      const int n_sel_pad = (n_sel + 15) & ~15;
-      const int s1 = choose_split(tiles_total * kMT1, kMaxSplit1, a.ctas, n_sel_pad, a.slab_rows);
-      const int s2 = choose_split(tiles_total * kMT2, kMaxSplit2, a.ctas, n_sel_pad, a.slab_rows);
       sc->status = (n_sel > a.rows_cap) ? kErrSchedOverflow : 0;
       sc->n_sel = n_sel;
       sc->n_sel_pad = n_sel_pad;
@@ -182,24 +222,38 @@ __device__ void permute_block(const PermuteArgs& a) {
     }
   }
   __syncthreads();
-  int running = s_offs[le];
-  const int ge = a.local_expert_offset + le;
-  for (int t0 = 0; t0 < a.T; t0 += 32) {
-    const int t = t0 + lane;
+  // phase 2: fill.  `base` (lane = expert) is this warp's next free row of each expert.
+  int base = s_wcount[warp][lane];
+  for (int c = c0; c < c1; ++c) {
+    const int t = c * 32 + lane;
     const uint32_t m = t < a.T ? a.local_mask[t] : 0u;
-    const bool mine = (m >> le) & 1u;
-    const uint32_t b = __ballot_sync(0xFFFFFFFFu, mine);
-    if (mine) {
-      const int row = running + __popc(b & lt_mask);
-      float w = 0.0f;
+    int idx[kTopK];
+    float wgt[kTopK];
+    if (m) {
 #pragma unroll
-      for (int k = 0; k < kTopK; ++k)
-        if (a.topk_idx[t * kTopK + k] == ge) w = a.topk_w[t * kTopK + k];
-      a.perm_token[row] = t;
-      a.perm_weight[row] = w;
-      a.tok_rows[t * kTopK + __popc(m & ((1u << le) - 1u))] = row;
+      for (int k = 0; k < kTopK; ++k) {
+        idx[k] = a.topk_idx[t * kTopK + k] - a.local_expert_offset;
+        wgt[k] = a.topk_w[t * kTopK + k];
+      }
     }
-    running += __popc(b);
+    int j = 0;                                  // rank of the expert among this token's local experts
+#pragma unroll
+    for (int le = 0; le < kELocal; ++le) {
+      const bool mine = (m >> le) & 1u;
+      const uint32_t b = __ballot_sync(0xFFFFFFFFu, mine);
+      const int first = __shfl_sync(0xFFFFFFFFu, base, le);
+      if (mine) {
+        const int row = first + __popc(b & lt_mask);
+        float w = 0.0f;
+#pragma unroll
+        for (int k = 0; k < kTopK; ++k) w = (idx[k] == le) ? wgt[k] : w;
+        a.perm_token[row] = t;
+        a.perm_weight[row] = w;
+        a.tok_rows[t * kTopK + j] = row;
+        ++j;
+      }
+      if (lane == le) base += __popc(b);
+    }
   }
 }
 
