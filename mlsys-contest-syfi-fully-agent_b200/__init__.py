@@ -10,6 +10,7 @@ Sub-modules:
   op      ``run(...)`` with the reference entry point's argument list
   ep      expert-parallel 256-expert layer over torch.distributed
   build   nvcc build of csrc/ for sm_100a
+  packaging  config.toml + solution.json in the reference's schema
 """
 from . import gen  # noqa: F401
 
@@ -17,7 +18,7 @@ from . import gen  # noqa: F401
 def __getattr__(name):
     # torch-free / CUDA-free modules are imported eagerly above; the ones that
     # need the compiled library are resolved on first use.
-    if name in ("loader", "op", "ep", "build"):
+    if name in ("loader", "op", "ep", "build", "packaging"):
         import importlib
         return importlib.import_module(f"{__name__}.{name}")
     raise AttributeError(name)

@@ -1,0 +1,99 @@
+// Device functions shared by the stand-alone SwiGLU / combine kernels and the
+// decode-fused GEMM kernels (which run them as a tail phase after a grid barrier).
+#pragma once
+#include <cuda_fp8.h>
+
+#include "kernels.h"
+
+namespace moe {
+
+__device__ __forceinline__ uint8_t to_e4m3(float x) {
+  return static_cast<uint8_t>(__nv_cvt_float_to_fp8(x, __NV_SATFINITE, __NV_E4M3));
+}
+__device__ __forceinline__ float from_e4m3(uint8_t b) {
+  const __half_raw h = __nv_cvt_fp8_to_halfraw(b, __NV_E4M3);
+  return __half2float(__half(h));
+}
+
+// SwiGLU + 4-term e4m3 split of one (row, 128-column block) by one warp; lane owns 4 columns.
+// `g1` points at the first split-K slab; slabs are `slab` floats apart.  Loads bypass L1
+// (the slabs may have been written by other SMs in the same kernel).
+__device__ __forceinline__ void swiglu_split_unit(const float* g1, size_t slab, int split, int row, int kb, int lane,
+                                                  uint8_t* cq, float* c_scale, int rows_cap) {
+  const float* p = g1 + static_cast<size_t>(row) * k2I + kb * kBlock + lane * 4;
+  float4 x1 = make_float4(0.f, 0.f, 0.f, 0.f), x2 = x1;
+  for (int s = 0; s < split; ++s) {
+    const float4 u = __ldcg(reinterpret_cast<const float4*>(p + s * slab));
+    const float4 v = __ldcg(reinterpret_cast<const float4*>(p + s * slab + kI));
+    x1.x += u.x; x1.y += u.y; x1.z += u.z; x1.w += u.w;
+    x2.x += v.x; x2.y += v.y; x2.z += v.z; x2.w += v.w;
+  }
+  float c[4];
+  c[0] = __fmul_rn(x2.x / (1.0f + expf(-x2.x)), x1.x);
+  c[1] = __fmul_rn(x2.y / (1.0f + expf(-x2.y)), x1.y);
+  c[2] = __fmul_rn(x2.z / (1.0f + expf(-x2.z)), x1.z);
+  c[3] = __fmul_rn(x2.w / (1.0f + expf(-x2.w)), x1.w);
+  float amax = fmaxf(fmaxf(fabsf(c[0]), fabsf(c[1])), fmaxf(fabsf(c[2]), fabsf(c[3])));
+#pragma unroll
+  for (int d = 16; d > 0; d >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, d));
+  // power-of-two scale with amax / scale in (224, 448]
+  int e = 0;
+  if (amax > 0.0f && amax < 3.0e38f) {
+    e = ilogbf(amax * (1.0f / 448.0f)) + 1;
+    e = max(-100, min(100, e));
+  }
+  const float scale = scalbnf(1.0f, e), inv = scalbnf(1.0f, -e);
+  uint32_t packed[kNTerms];
+#pragma unroll
+  for (int t = 0; t < kNTerms; ++t) packed[t] = 0;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    float r = c[i] * inv;
+    if (!(fabsf(r) <= 448.0f)) r = r > 0.0f ? 448.0f : (r < 0.0f ? -448.0f : 0.0f);   // inf / nan guard
+#pragma unroll
+    for (int t = 0; t < kNTerms; ++t) {
+      const uint8_t q = to_e4m3(r);
+      r -= from_e4m3(q);
+      packed[t] |= static_cast<uint32_t>(q) << (8 * i);
+    }
+  }
+#pragma unroll
+  for (int t = 0; t < kNTerms; ++t)
+    *reinterpret_cast<uint32_t*>(cq + (static_cast<size_t>(t) * rows_cap + row) * kI + kb * kBlock + lane * 4) =
+        packed[t];
+  if (lane == 0) c_scale[static_cast<size_t>(row) * kKB2 + kb] = scale;
+}
+
+__device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
+  uint32_t r;
+  asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+  return r;
+}
+
+// Weighted combine of 4 output columns of one token: the token's local experts in ascending
+// order, each the sum of its GEMM2 split-K slabs, multiply then add (the definition's
+// index_add_(O * w), references/moe.py:196-200), bf16 round-to-nearest-even.
+__device__ __forceinline__ void combine_unit(const float* o, size_t slab, int split, int n_local, const int* rows,
+                                             const float* perm_weight, int c, uint16_t* out_row) {
+  float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+  for (int j = 0; j < n_local; ++j) {
+    const int row = rows[j];
+    const float w = perm_weight[row];
+    const float* p = o + static_cast<size_t>(row) * kH + c * 4;
+    float4 v = __ldcg(reinterpret_cast<const float4*>(p));
+    for (int s = 1; s < split; ++s) {
+      const float4 u = __ldcg(reinterpret_cast<const float4*>(p + s * slab));
+      v.x += u.x; v.y += u.y; v.z += u.z; v.w += u.w;
+    }
+    acc.x = __fadd_rn(acc.x, __fmul_rn(v.x, w));
+    acc.y = __fadd_rn(acc.y, __fmul_rn(v.y, w));
+    acc.z = __fadd_rn(acc.z, __fmul_rn(v.z, w));
+    acc.w = __fadd_rn(acc.w, __fmul_rn(v.w, w));
+  }
+  uint2 q;
+  q.x = pack_bf16x2(acc.x, acc.y);
+  q.y = pack_bf16x2(acc.z, acc.w);
+  *reinterpret_cast<uint2*>(out_row + c * 4) = q;
+}
+
+}  // namespace moe

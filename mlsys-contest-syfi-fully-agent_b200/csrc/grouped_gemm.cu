@@ -34,8 +34,10 @@
 // device-resident schedule; CTAs are persistent and take items round-robin.
 // Every mbarrier wait is bounded (ptx.cuh); on a timeout the CTA records an error
 // bit in the schedule block and leaves through the normal teardown.
+#include "epilogue_device.cuh"
 #include "kernels.h"
 #include "ptx.cuh"
+#include "route_device.cuh"
 
 namespace moe {
 
@@ -78,7 +80,7 @@ struct Cfg {
   static constexpr int STAGE_BYTES = KPS * KB_BYTES;
   static constexpr int SC_BUFS = N_TILE <= 32 ? 2 : 1;                  // scale-product tables
   static constexpr int SC_BYTES = SC_BUFS * KB * N_TILE * 4;
-  static constexpr int AUX_BYTES = 1024;
+  static constexpr int AUX_BYTES = 1024 + 4096;                         // Aux + FusedAux
   static constexpr int BUDGET = 227 * 1024 - 1024;   // 1 KB slack for the 1024-byte alignment of the ring
   static constexpr int STAGES_FIT = (BUDGET - SC_BYTES - AUX_BYTES) / STAGE_BYTES;
   static constexpr int STAGES = STAGES_FIT > 10 ? 10 : STAGES_FIT;
@@ -102,6 +104,44 @@ struct Aux {
   int offs[kELocal + 1];
 };
 static_assert(sizeof(Aux) <= 1024, "Aux must fit its slot");
+
+// Extra shared state of the decode-fused kernels: every CTA routes all (<= 16) tokens itself.
+struct FusedAux {
+  float bias[kEGlobal];
+  int tidx[kFusedMaxTokens][kTopK];
+  float tw[kFusedMaxTokens][kTopK];
+  uint32_t mask[kFusedMaxTokens];     // per token: selected local experts
+  uint32_t colmask[kELocal];          // per local expert: tokens that selected it
+  int items, split, n_sel_pad, n_sel;
+};
+static_assert(sizeof(FusedAux) <= 4096, "FusedAux must fit its slot");
+
+// Grid-wide barrier for a grid whose CTAs are all resident (one per SM).  The 64-bit word holds
+// {arrivals, call tag}.  CTA 0 installs {0, tag} when the kernel starts (after the wait on earlier
+// kernels, long before anybody arrives); an arriving CTA first checks that the tag is the current
+// call's, then adds one, then waits for `n` arrivals.  So the word needs no initialisation by the
+// caller and no reset between calls, and an arrival is one atomic add.  Bounded like every other
+// wait here: false on timeout.
+__device__ __forceinline__ void grid_barrier_init(unsigned int* word2, unsigned int tag) {
+  atomicExch(reinterpret_cast<unsigned long long*>(word2), static_cast<unsigned long long>(tag) << 32);
+}
+
+__device__ __forceinline__ bool grid_barrier(unsigned int* word2, unsigned int tag, unsigned int n) {
+  unsigned long long* word = reinterpret_cast<unsigned long long*>(word2);
+  __threadfence();
+  const uint64_t t0 = globaltimer_ns();
+  unsigned int spins = 0;
+  while (static_cast<unsigned int>(*reinterpret_cast<volatile unsigned long long*>(word) >> 32) != tag)
+    if ((++spins & 0xFFu) == 0 && globaltimer_ns() - t0 > MOE_WAIT_LIMIT_NS) return false;
+  atomicAdd(word, 1ull);
+  while (true) {
+    const unsigned long long v = *reinterpret_cast<volatile unsigned long long*>(word);
+    if (static_cast<unsigned int>(v) >= n) break;
+    if ((++spins & 0xFFu) == 0 && globaltimer_ns() - t0 > MOE_WAIT_LIMIT_NS) return false;
+  }
+  __threadfence();
+  return true;
+}
 
 struct Item {
   int e, m, s, row0, valid, kb0, kb1;
@@ -148,7 +188,7 @@ __device__ __forceinline__ void tmem_ld_cols(uint32_t taddr, float* v) {
   }
 }
 
-template <int GEMM, int N_TILE>
+template <int GEMM, int N_TILE, bool FUSED = false>
 __global__ void __launch_bounds__(kThreads, 1)
 grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_b, GemmArgs a) {
   using C = Cfg<GEMM, N_TILE>;
@@ -183,12 +223,118 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
     tmem_relinquish();
   }
   griddep_wait();   // the schedule, the operands and the output slabs belong to earlier kernels until here
-  const int items = GEMM == 1 ? sched->items1 : sched->items2;
-  const int split = GEMM == 1 ? sched->split1 : sched->split2;
-  const int n_sel_pad = sched->n_sel_pad;
-  if (threadIdx.x <= kELocal) {
-    aux->prefix[threadIdx.x] = sched->tile_prefix[threadIdx.x];
-    aux->offs[threadIdx.x] = sched->offs[threadIdx.x];
+  if (threadIdx.x == 0) TRACE(3, 5);
+  if (FUSED && blockIdx.x == 0 && threadIdx.x == 0) grid_barrier_init(GEMM == 1 ? sched->bar1 : sched->bar2, a.call_tag);
+  int items, split, n_sel_pad;
+  FusedAux* fa = reinterpret_cast<FusedAux*>(reinterpret_cast<uint8_t*>(aux) + 1024);
+  if constexpr (FUSED && GEMM == 1) {
+    // Decode path: no routing / permutation / gather kernels ran.  Every CTA routes all tokens and
+    // derives the same schedule in shared memory; CTA 0 also publishes it for the later kernel.
+    static_assert(N_TILE == kFusedMaxTokens, "the fused path puts every token in one token tile");
+    for (int i = threadIdx.x; i < kEGlobal; i += kThreads)
+      fa->bias[i] = __uint_as_float(static_cast<uint32_t>(a.bias_bf16[i]) << 16);
+    __syncthreads();
+    if (threadIdx.x == 0) TRACE(3, 6);
+    for (int t = warp; t < a.T; t += kThreads / 32) {
+      int idx;
+      float w;
+      route_token(a.logits + static_cast<size_t>(t) * kEGlobal, fa->bias, a.routed_scaling_factor, lane, idx, w);
+      uint32_t bit = 0;
+      if (lane < kTopK) {
+        fa->tidx[t][lane] = idx;
+        fa->tw[t][lane] = w;
+        const int le = idx - a.local_expert_offset;
+        if (le >= 0 && le < kELocal) bit = 1u << le;
+      }
+      bit = __reduce_or_sync(0xFFFFFFFFu, bit);
+      if (lane == 0) fa->mask[t] = bit;
+    }
+    if (threadIdx.x == 0) TRACE(3, 7);
+    __syncthreads();
+    if (threadIdx.x == 0) TRACE(3, 8);
+    if (warp == 0) {                     // lane = local expert
+      uint32_t cm = 0;
+      for (int t = 0; t < a.T; ++t) cm |= ((fa->mask[t] >> lane) & 1u) << t;
+      const int c = __popc(cm);
+      int inc = c, tinc = c > 0 ? 1 : 0;
+#pragma unroll
+      for (int d = 1; d < 32; d <<= 1) {
+        const int v = __shfl_up_sync(0xFFFFFFFFu, inc, d);
+        const int tv = __shfl_up_sync(0xFFFFFFFFu, tinc, d);
+        if (lane >= d) { inc += v; tinc += tv; }
+      }
+      fa->colmask[lane] = cm;
+      aux->offs[lane + 1] = inc;
+      aux->prefix[lane + 1] = tinc;
+      const uint32_t act = __ballot_sync(0xFFFFFFFFu, c > 0);
+      const int n_sel = __shfl_sync(0xFFFFFFFFu, inc, 31), tiles_total = __shfl_sync(0xFFFFFFFFu, tinc, 31);
+      const int pad = (n_sel + 15) & ~15;
+      const int s1 = choose_split_warp(tiles_total * kMT1, kMaxSplit1, a.ctas, pad, a.slab_rows, lane, kKB1,
+                                       Cfg<1, kFusedMaxTokens>::KPS);
+      const int s2 = choose_split_warp(tiles_total * kMT2, kMaxSplit2, a.ctas, pad, a.slab_rows, lane, kKB2,
+                                       Cfg<2, kFusedMaxTokens>::KPS);
+      if (lane == 0) {
+        aux->offs[0] = 0;
+        aux->prefix[0] = 0;
+        fa->items = tiles_total * kMT1 * s1;
+        fa->split = s1;
+        fa->n_sel_pad = pad;
+        fa->n_sel = n_sel;
+      }
+      if (blockIdx.x == 0) {
+        sched->counts[lane] = c;
+        sched->offs[lane + 1] = inc;
+        sched->tile_prefix[lane + 1] = tinc;
+        if (lane == 0) {
+          sched->offs[0] = 0;
+          sched->tile_prefix[0] = 0;
+          sched->status = 0;
+          sched->n_sel = n_sel;
+          sched->n_sel_pad = pad;
+          sched->n_active = __popc(act);
+          sched->n_tile = N_TILE;
+          sched->tiles_total = tiles_total;
+          sched->split1 = s1;
+          sched->split2 = s2;
+          sched->items1 = tiles_total * kMT1 * s1;
+          sched->items2 = tiles_total * kMT2 * s2;
+        }
+      }
+    }
+    __syncthreads();
+    if (blockIdx.x == 0 && warp == 2 && lane < a.T) {   // lane = token: selection, permutation, row lists
+      const int t = lane;
+      const uint32_t m = fa->mask[t];
+      a.local_mask[t] = m;
+#pragma unroll
+      for (int k = 0; k < kTopK; ++k) {
+        a.topk_idx[t * kTopK + k] = fa->tidx[t][k];
+        a.topk_w[t * kTopK + k] = fa->tw[t][k];
+      }
+      int j = 0;
+      for (uint32_t rest = m; rest; rest &= rest - 1, ++j) {
+        const int le = __ffs(rest) - 1;
+        const int row = aux->offs[le] + __popc(fa->colmask[le] & ((1u << t) - 1u));
+        float w = 0.0f;
+#pragma unroll
+        for (int k = 0; k < kTopK; ++k)
+          if (fa->tidx[t][k] - a.local_expert_offset == le) w = fa->tw[t][k];
+        a.perm_token[row] = t;
+        a.perm_weight[row] = w;
+        a.tok_rows[t * kTopK + j] = row;
+      }
+    }
+    items = fa->items;
+    split = fa->split;
+    n_sel_pad = fa->n_sel_pad;
+  } else {
+    items = GEMM == 1 ? sched->items1 : sched->items2;
+    split = GEMM == 1 ? sched->split1 : sched->split2;
+    n_sel_pad = sched->n_sel_pad;
+    if (threadIdx.x <= kELocal) {
+      aux->prefix[threadIdx.x] = sched->tile_prefix[threadIdx.x];
+      aux->offs[threadIdx.x] = sched->offs[threadIdx.x];
+    }
   }
   tc_fence_before_sync();
   __syncthreads();
@@ -214,11 +360,12 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
           const uint32_t dst = smem_u32(smem + stage * C::STAGE_BYTES);
           // weights: [KPS][128 rows][128 B]; tokens: [KPS][NTERMS planes][N_TILE rows][128 B]
           tma_load_3d(dst, &tm_w, 0, wy, kb, bar);
-          if (GEMM == 1) tma_load_3d(dst + C::KPS * C::A_BYTES, &tm_b, 0, w.row0, kb, bar);
+          if (GEMM == 1) tma_load_3d(dst + C::KPS * C::A_BYTES, &tm_b, 0, FUSED ? 0 : w.row0, kb, bar);
           else tma_load_4d(dst + C::KPS * C::A_BYTES, &tm_b, 0, w.row0, 0, kb, bar);
         }
       }
     }
+    __syncwarp();   // block-wide barriers below need whole warps
   } else if (warp == 1) {
     // ------------------------------------------------------------------ UMMA issuer
     if (lane == 0) {
@@ -260,6 +407,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
         }
       }
     }
+    __syncwarp();
   } else {
     // ------------------------------------------------------------------ promotion + epilogue (warps 2..9)
     const int q = warp & 3;                       // TMEM lane quarter this warp may access
@@ -283,8 +431,12 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
       const int nkb = w.kb1 - w.kb0;
       if (idx >= nkb * N_TILE) return 0.0f;
       const int kbl = idx / N_TILE, j = idx % N_TILE, kb = w.kb0 + kbl;
-      if (j >= w.valid) return 0.0f;
       const float ws = __ldg(a.w_scale + (static_cast<size_t>(w.e) * C::MT + w.m) * C::KB + kb);
+      if constexpr (FUSED && GEMM == 1) {      // column j is token j; the scale table is the definition's [56, T]
+        if (!((fa->colmask[w.e] >> j) & 1u)) return 0.0f;
+        return ws * __ldg(a.hidden_scale + static_cast<size_t>(kb) * a.T + j);
+      }
+      if (j >= w.valid) return 0.0f;
       return ws * __ldg(a.b_scale + static_cast<size_t>(w.row0 + j) * C::KB + kb);
     };
     float pre[C::SC_BUFS == 2 ? kMaxE : 1];
@@ -361,11 +513,21 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
           }
       }
       if (!ok) break;
-      float* out = a.out + (static_cast<size_t>(w.s) * n_sel_pad + w.row0 + h * C::CPW) * C::M_TOTAL + w.m * 128 +
-                   q * 32 + lane;
+      if constexpr (FUSED && GEMM == 1) {      // token columns -> the expert's rows (ascending token)
+        const uint32_t cm = fa->colmask[w.e];
+        float* out = a.out + (static_cast<size_t>(w.s) * n_sel_pad + w.row0) * C::M_TOTAL + w.m * 128 + q * 32 + lane;
 #pragma unroll
-      for (int j = 0; j < C::CPW; ++j)
-        if (h * C::CPW + j < w.valid) out[static_cast<size_t>(j) * C::M_TOTAL] = acc[j];
+        for (int j = 0; j < C::CPW; ++j) {
+          const int col = h * C::CPW + j;
+          if ((cm >> col) & 1u) out[static_cast<size_t>(__popc(cm & ((1u << col) - 1u))) * C::M_TOTAL] = acc[j];
+        }
+      } else {
+        float* out = a.out + (static_cast<size_t>(w.s) * n_sel_pad + w.row0 + h * C::CPW) * C::M_TOTAL + w.m * 128 +
+                     q * 32 + lane;
+#pragma unroll
+        for (int j = 0; j < C::CPW; ++j)
+          if (h * C::CPW + j < w.valid) out[static_cast<size_t>(j) * C::M_TOTAL] = acc[j];
+      }
       if (C::SC_BUFS == 2 && inext < items) {
         float* scn = sc_base + ((nitem + 1) & 1u) * (C::KB * N_TILE);
 #pragma unroll
@@ -375,11 +537,41 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
         }
       }
     }
+    if constexpr (FUSED) {
+      // Tail phase of the decode path.  All CTAs are resident (one per SM), so a grid barrier is safe;
+      // after it every split-K slab of this GEMM is complete and the next stage runs here instead of
+      // in a kernel of its own: SwiGLU + e4m3 split after GEMM1, weighted combine + bf16 cast after GEMM2.
+      __threadfence();
+      epi_sync();
+      if (etid == 0) TRACE(3, 3);
+      if (ok && etid == 0 && !grid_barrier(GEMM == 1 ? sched->bar1 : sched->bar2, a.call_tag, gridDim.x)) *abort_flag = 1;
+      epi_sync();
+      if (etid == 0) TRACE(3, 4);
+      if (ok && !*abort_flag) {
+        if constexpr (GEMM == 1) {
+          const int units = fa->n_sel * kKB2;
+          const size_t slab = static_cast<size_t>(n_sel_pad) * k2I;
+          for (int u = blockIdx.x * kEpiWarps + (warp - 2); u < units; u += gridDim.x * kEpiWarps)
+            swiglu_split_unit(a.out, slab, split, u / kKB2, u % kKB2, lane, a.cq, a.c_scale, a.rows_cap);
+        } else {
+          constexpr int kVec = kH / 4;
+          const size_t slab = static_cast<size_t>(n_sel_pad) * kH;
+          const int total = a.T * kVec;
+          for (int i = blockIdx.x * kEpiThreads + etid; i < total; i += gridDim.x * kEpiThreads) {
+            const int t = i / kVec, c = i % kVec;
+            combine_unit(a.out, slab, split, __popc(a.local_mask[t]), a.tok_rows + t * kTopK, a.perm_weight, c,
+                         a.out_bf16 + static_cast<size_t>(t) * kH);
+          }
+        }
+      }
+    }
   }
 
   tc_fence_before_sync();
   __syncthreads();
   if (threadIdx.x == 0) TRACE(3, 2);
+  if (threadIdx.x == 64) TRACE(3, 9);
+  if (threadIdx.x == 32) TRACE(3, 10);
   if (threadIdx.x == 0 && aux->abort) atomicOr(&sched->status, GEMM == 1 ? kErrGemm1Timeout : kErrGemm2Timeout);
   if (warp == 1) {
     __syncwarp();
@@ -393,6 +585,20 @@ int launch_one(const CUtensorMap& tm_w, const CUtensorMap& tm_b, const GemmArgs&
   using C = Cfg<GEMM, N_TILE>;
   return static_cast<int>(launch_pdl(grouped_gemm_kernel<GEMM, N_TILE>, dim3(ctas), dim3(kThreads), C::SMEM_BYTES,
                                      stream, tm_w, tm_b, a));
+}
+
+template <int GEMM>
+int launch_fused(const CUtensorMap& tm_w, const CUtensorMap& tm_b, const GemmArgs& a, int ctas, cudaStream_t stream) {
+  using C = Cfg<GEMM, kFusedMaxTokens>;
+  return static_cast<int>(launch_pdl(grouped_gemm_kernel<GEMM, kFusedMaxTokens, true>, dim3(ctas), dim3(kThreads),
+                                     C::SMEM_BYTES, stream, tm_w, tm_b, a));
+}
+
+template <int GEMM>
+int init_fused() {
+  using C = Cfg<GEMM, kFusedMaxTokens>;
+  return static_cast<int>(cudaFuncSetAttribute(grouped_gemm_kernel<GEMM, kFusedMaxTokens, true>,
+                                               cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES));
 }
 
 template <int GEMM, int N_TILE>
@@ -429,7 +635,14 @@ int grouped_gemm_init() {
   if ((rc = init_one<2, 32>())) return rc;
   if ((rc = init_one<2, 64>())) return rc;
   if ((rc = init_one<2, 128>())) return rc;
+  if ((rc = init_fused<1>())) return rc;
+  if ((rc = init_fused<2>())) return rc;
   return 0;
+}
+
+int launch_fused_gemm(int gemm_id, const CUtensorMap& tm_w, const CUtensorMap& tm_b, const GemmArgs& a, int ctas,
+                      cudaStream_t stream) {
+  return gemm_id == 1 ? launch_fused<1>(tm_w, tm_b, a, ctas, stream) : launch_fused<2>(tm_w, tm_b, a, ctas, stream);
 }
 
 int launch_grouped_gemm(int gemm_id, int n_tile, const CUtensorMap& tm_w, const CUtensorMap& tm_b, const GemmArgs& a,

@@ -52,6 +52,7 @@ struct PermuteArgs {
   int local_expert_offset;
   int n_tile;                   // token-tile width the GEMMs will use
   int ctas;                     // persistent CTAs the GEMMs will run
+  int kps1, kps2;               // K-blocks per pipeline stage of the two GEMM kernels (split granularity)
   int rows_cap, slab_rows;
   const uint32_t* local_mask;
   const int* topk_idx;
@@ -80,6 +81,18 @@ struct GemmArgs {
   const float* w_scale;         // [32, M/128, K/128]
   const float* b_scale;         // per-row scales, row-major: GEMM1 [rows, 56]; GEMM2 [rows, 16]
   float* out;                   // fp32 slabs [split][n_sel_pad, M]
+  // ---- only read by the decode-fused kernels (T <= 16), see grouped_gemm.cu
+  const float* logits;          // [T, 256]
+  const uint16_t* bias_bf16;    // [256]
+  const float* hidden_scale;    // [56, T]
+  int T, local_expert_offset;
+  float routed_scaling_factor;
+  int ctas, rows_cap, slab_rows;
+  unsigned int call_tag;        // distinct per call: tags the grid barrier words
+  int* topk_idx; float* topk_w; uint32_t* local_mask;
+  int* perm_token; float* perm_weight; int* tok_rows;
+  uint8_t* cq; float* c_scale;  // SwiGLU planes written by the fused GEMM1 tail
+  uint16_t* out_bf16;           // final output written by the fused GEMM2 tail
 };
 
 struct SwigluArgs {
@@ -106,6 +119,10 @@ void launch_gather_rows(const GatherArgs& a, int T, cudaStream_t stream);
 // gemm_id 1 or 2; n_tile in {16, 32, 64, 128}.  Returns a cudaError_t as int.
 int launch_grouped_gemm(int gemm_id, int n_tile, const CUtensorMap& tm_w, const CUtensorMap& tm_b, const GemmArgs& a,
                         int ctas, cudaStream_t stream);
+// Decode path (T <= 16): GEMM1 with in-kernel routing and a SwiGLU tail, GEMM2 with a combine tail.
+int launch_fused_gemm(int gemm_id, const CUtensorMap& tm_w, const CUtensorMap& tm_b, const GemmArgs& a, int ctas,
+                      cudaStream_t stream);
+constexpr int kFusedMaxTokens = 16;
 int grouped_gemm_kblocks_per_stage(int gemm_id, int n_tile);   // K-blocks one TMA box of that kernel brings
 int grouped_gemm_init();   // one-time function attributes (dynamic shared memory opt-in)
 void launch_swiglu_split(const SwigluArgs& a, int T, cudaStream_t stream);

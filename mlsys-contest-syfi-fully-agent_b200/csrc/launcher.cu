@@ -193,6 +193,14 @@ int pick_n_tile(int T) {
   return T <= 16 ? 16 : T <= 32 ? 32 : T <= 64 ? 64 : 128;
 }
 
+bool use_fused_decode() {
+  static const bool on = [] {
+    const char* s = std::getenv("MOE_B200_FUSED_DECODE");
+    return !(s && s[0] == '0');
+  }();
+  return on;
+}
+
 bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
 }  // namespace
@@ -281,9 +289,36 @@ extern "C" int moe_fp8_block_scale_run(const float* routing_logits, const uint16
   if ((rc = get_map(dev, kblock_map(a_packed, L.rows_cap, kH, n_tile, kps1), &tm_a))) return rc;
   if ((rc = get_map(dev, planes_map(cq, L.rows_cap, n_tile, kps2), &tm_c))) return rc;
 
+  if (T <= kFusedMaxTokens && use_fused_decode()) {
+    // Decode path: two launches.  GEMM1 routes in-kernel, reads the token rows straight from
+    // hidden_states (all tokens are one token tile) and ends with SwiGLU; GEMM2 ends with the combine.
+    static std::atomic<unsigned int> call_counter{0x9E3779B1u};
+    CUtensorMap tm_h;
+    if ((rc = get_map(dev, kblock_map(hidden_states, static_cast<uint64_t>(T), kH, kFusedMaxTokens, kps1), &tm_h)))
+      return rc;
+    GemmArgs fa{};
+    fa.sched = sched; fa.w_scale = gemm1_weights_scale; fa.b_scale = nullptr; fa.out = g1;
+    fa.logits = routing_logits; fa.bias_bf16 = routing_bias; fa.hidden_scale = hidden_states_scale;
+    fa.T = T; fa.local_expert_offset = local_expert_offset; fa.routed_scaling_factor = routed_scaling_factor;
+    fa.ctas = ctas; fa.rows_cap = L.rows_cap; fa.slab_rows = L.slab_rows;
+    fa.call_tag = call_counter.fetch_add(2654435761u) | 1u;
+    fa.topk_idx = topk_idx; fa.topk_w = topk_w; fa.local_mask = local_mask;
+    fa.perm_token = perm_token; fa.perm_weight = perm_weight; fa.tok_rows = tok_rows;
+    fa.cq = cq; fa.c_scale = c_scale; fa.out_bf16 = output;
+    stage_mark(0, stream); stage_mark(1, stream); stage_mark(2, stream);
+    if ((rc = launch_fused_gemm(1, tm_w13, tm_h, fa, ctas, stream))) { g_last_cuda_error = rc; return MOE_B200_ECUDA; }
+    stage_mark(3, stream); stage_mark(4, stream);
+    GemmArgs fb = fa;
+    fb.w_scale = gemm2_weights_scale; fb.b_scale = c_scale; fb.out = o;
+    if ((rc = launch_fused_gemm(2, tm_w2, tm_c, fb, ctas, stream))) { g_last_cuda_error = rc; return MOE_B200_ECUDA; }
+    stage_mark(5, stream); stage_mark(6, stream);
+    g_launches += 2;
+    return MOE_B200_OK;
+  }
+
   RouteArgs ra{routing_logits, routing_bias, T, local_expert_offset, routed_scaling_factor, topk_idx, topk_w,
                local_mask};
-  PermuteArgs pa{T, local_expert_offset, n_tile, ctas, L.rows_cap, L.slab_rows, local_mask, topk_idx, topk_w,
+  PermuteArgs pa{T, local_expert_offset, n_tile, ctas, static_cast<int>(kps1), static_cast<int>(kps2), L.rows_cap, L.slab_rows, local_mask, topk_idx, topk_w,
                  sched, perm_token, perm_weight, tok_rows};
   stage_mark(0, stream);
   launch_route_permute(ra, pa, stream);
@@ -297,7 +332,8 @@ extern "C" int moe_fp8_block_scale_run(const float* routing_logits, const uint16
   g_launches += 1;
   stage_mark(2, stream);
 
-  GemmArgs g1a{sched, gemm1_weights_scale, a_scale_rows, g1};
+  GemmArgs g1a{};
+  g1a.sched = sched; g1a.w_scale = gemm1_weights_scale; g1a.b_scale = a_scale_rows; g1a.out = g1;
   if ((rc = launch_grouped_gemm(1, n_tile, tm_w13, tm_a, g1a, ctas, stream))) {
     g_last_cuda_error = rc;
     return MOE_B200_ECUDA;
@@ -311,7 +347,8 @@ extern "C" int moe_fp8_block_scale_run(const float* routing_logits, const uint16
   g_launches += 1;
   stage_mark(4, stream);
 
-  GemmArgs g2a{sched, gemm2_weights_scale, c_scale, o};
+  GemmArgs g2a{};
+  g2a.sched = sched; g2a.w_scale = gemm2_weights_scale; g2a.b_scale = c_scale; g2a.out = o;
   if ((rc = launch_grouped_gemm(2, n_tile, tm_w2, tm_c, g2a, ctas, stream))) {
     g_last_cuda_error = rc;
     return MOE_B200_ECUDA;

@@ -47,7 +47,9 @@ struct MoeSched {
   int tiles_total;         // sum over experts of ceil(count / n_tile)
   int split1, split2;      // split-K factors chosen for GEMM1 / GEMM2
   int items1, items2;      // work items of GEMM1 / GEMM2
-  int pad_[6];
+  unsigned int bar1[2];    // grid barrier of the fused GEMM1 kernel: {arrivals, call tag}
+  unsigned int bar2[2];    // same for the fused GEMM2 kernel
+  int pad_[2];
   int counts[kELocal];
   int offs[kELocal + 1];       // exclusive prefix of counts
   int tile_prefix[kELocal + 1];  // exclusive prefix of token tiles

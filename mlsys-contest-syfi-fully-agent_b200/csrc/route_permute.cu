@@ -12,82 +12,11 @@
 //   and the atomics-ordered perm_fill_kernel (moe.cu:217-309), and also builds the
 //   split-K schedule on the device so that no regime needs a host round trip.
 #include "kernels.h"
+#include "route_device.cuh"
 
 namespace moe {
 
 namespace {
-
-__device__ __forceinline__ uint32_t order_key(float f) {
-  uint32_t u = __float_as_uint(f);
-  return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
-}
-
-// Routes token t with the calling warp.  On return lanes 0..7 hold the selected
-// global expert (descending biased score) and its combination weight.
-__device__ __forceinline__ void route_token(const float* __restrict__ logits_row, const float* bias_smem,
-                                            float routed_scaling_factor, int lane, int& sel_idx, float& sel_w) {
-  float s[kNGroup];
-  uint32_t key[kNGroup];
-#pragma unroll
-  for (int g = 0; g < kNGroup; ++g) {
-    const float x = logits_row[g * 32 + lane];
-    s[g] = 1.0f / (1.0f + expf(-x));
-    key[g] = order_key(s[g] + bias_smem[g * 32 + lane]);
-  }
-  // group score = sum of the two largest biased scores of the group
-  float gscore[kNGroup];
-#pragma unroll
-  for (int g = 0; g < kNGroup; ++g) {
-    const uint32_t k1 = __reduce_max_sync(0xFFFFFFFFu, key[g]);
-    const uint32_t who = __ballot_sync(0xFFFFFFFFu, key[g] == k1);
-    const int first = __ffs(who) - 1;
-    const uint32_t k2 = __reduce_max_sync(0xFFFFFFFFu, lane == first ? 0u : key[g]);
-    // undo the order-preserving map
-    const uint32_t u1 = (k1 & 0x80000000u) ? (k1 & 0x7FFFFFFFu) : ~k1;
-    const uint32_t u2 = (k2 & 0x80000000u) ? (k2 & 0x7FFFFFFFu) : ~k2;
-    gscore[g] = __uint_as_float(u1) + __uint_as_float(u2);
-  }
-  // keep the 4 best groups (ties: lower group index first)
-  uint32_t keep = 0;
-#pragma unroll
-  for (int g = 0; g < kNGroup; ++g) {
-    int rank = 0;
-#pragma unroll
-    for (int h = 0; h < kNGroup; ++h) rank += (gscore[h] > gscore[g]) || (gscore[h] == gscore[g] && h < g);
-    keep |= (rank < kTopKGroup ? 1u : 0u) << g;
-  }
-  // 8 rounds of warp-wide arg-max over the kept candidates (ties: lower expert index first)
-  uint32_t avail = keep;
-  sel_idx = -1;
-  float sel_s = 0.0f;
-#pragma unroll
-  for (int r = 0; r < kTopK; ++r) {
-    uint32_t bk = 0;
-    int bg = 0;
-#pragma unroll
-    for (int g = kNGroup - 1; g >= 0; --g) {
-      const bool ok = (avail >> g) & 1u;
-      if (ok && key[g] >= bk) { bk = key[g]; bg = g; }   // descending g with >= keeps the lowest g on ties
-    }
-    const bool has = avail != 0;
-    const uint32_t kmax = __reduce_max_sync(0xFFFFFFFFu, has ? bk : 0u);
-    const uint32_t cand = (has && bk == kmax) ? static_cast<uint32_t>(bg * 32 + lane) : 0xFFFFFFFFu;
-    const uint32_t win = __reduce_min_sync(0xFFFFFFFFu, cand);
-    const int wl = win & 31, wg = win >> 5;
-    float sv = 0.0f;
-#pragma unroll
-    for (int g = 0; g < kNGroup; ++g) sv = (g == wg) ? s[g] : sv;
-    sv = __shfl_sync(0xFFFFFFFFu, sv, wl);
-    if (lane == wl) avail &= ~(1u << wg);
-    if (lane == r) { sel_idx = static_cast<int>(win); sel_s = sv; }
-  }
-  // weights: s / (sum of the 8 selected s + 1e-20) * factor  (references/moe.py:154-158)
-  float sum = 0.0f;
-#pragma unroll
-  for (int k = 0; k < kTopK; ++k) sum += __shfl_sync(0xFFFFFFFFu, sel_s, k);
-  sum += 1e-20f;
-  sel_w = (sel_s / sum) * routed_scaling_factor;
-}
 
 __device__ __forceinline__ void route_tokens_strided(const RouteArgs& a, const float* bias_smem, int first_token,
                                                      int token_stride, int lane) {
@@ -112,42 +41,6 @@ __device__ __forceinline__ void load_bias(const uint16_t* bias_bf16, float* bias
     bias_smem[i] = __uint_as_float(static_cast<uint32_t>(bias_bf16[i]) << 16);
 }
 
-// Best split-K factor for `tiles` equal work items on `ctas` persistent CTAs:
-// the smallest S whose last wave is fullest (within 4 %), subject to the slab capacity.
-__device__ int choose_split(int tiles, int max_split, int ctas, int n_sel_pad, int slab_rows) {
-  if (tiles <= 0) return 1;
-  int best = 1;
-  float best_eff = 0.0f;
-  for (int S = 1; S <= max_split; ++S) {
-    if (static_cast<long long>(S) * n_sel_pad > slab_rows) break;
-    const int items = tiles * S;
-    const int waves = (items + ctas - 1) / ctas;
-    const float eff = static_cast<float>(items) / static_cast<float>(waves * ctas);
-    if (eff > best_eff * 1.04f) { best_eff = eff; best = S; }
-  }
-  return best;
-}
-
-// Best split-K factors, evaluated one candidate per lane.
-__device__ int choose_split_warp(int tiles, int max_split, int ctas, int n_sel_pad, int slab_rows, int lane) {
-  if (tiles <= 0) return 1;
-  const int S = lane + 1;
-  float eff = 0.0f;
-  if (S <= max_split && static_cast<long long>(S) * n_sel_pad <= slab_rows) {
-    const int items = tiles * S;
-    const int waves = (items + ctas - 1) / ctas;
-    eff = static_cast<float>(items) / static_cast<float>(waves * ctas);
-  }
-  // same rule as choose_split: walk S upwards, move on only for a > 4 % fuller last wave
-  int best = 1;
-  float best_eff = 0.0f;
-  for (int k = 0; k < max_split; ++k) {
-    const float e = __shfl_sync(0xFFFFFFFFu, eff, k);
-    if (e > best_eff * 1.04f) { best_eff = e; best = k + 1; }
-  }
-  return best;
-}
-
 // Block-wide (1024 threads) histogram, scan, stable permutation and schedule.  Warp w owns
 // the contiguous token range [w * span, (w + 1) * span); inside a 32-token chunk lane = token.
 // Phase 1 counts, per warp and expert, the tokens that selected the expert; an exclusive
@@ -156,7 +49,6 @@ __device__ int choose_split_warp(int tiles, int max_split, int ctas, int n_sel_p
 // Requires the routing outputs of all T tokens to be visible.
 __device__ void permute_block(const PermuteArgs& a) {
   __shared__ int s_wcount[32][kELocal + 1];     // [warp][expert]: count, then first row (+1: no bank conflicts)
-  __shared__ int s_offs[kELocal + 1];
   const int lane = threadIdx.x & 31;
   const int warp = threadIdx.x >> 5;
   const uint32_t lt_mask = (1u << lane) - 1u;
@@ -196,17 +88,15 @@ __device__ void permute_block(const PermuteArgs& a) {
       run += n;
     }
     MoeSched* sc = a.sched;
-    s_offs[lane + 1] = inc;
     sc->counts[lane] = c;
     sc->offs[lane + 1] = inc;
     sc->tile_prefix[lane + 1] = tinc;
     const uint32_t act = __ballot_sync(0xFFFFFFFFu, c > 0);
     const int n_sel = __shfl_sync(0xFFFFFFFFu, inc, 31), tiles_total = __shfl_sync(0xFFFFFFFFu, tinc, 31);
     const int n_sel_pad = (n_sel + 15) & ~15;
-    const int s1 = choose_split_warp(tiles_total * kMT1, kMaxSplit1, a.ctas, n_sel_pad, a.slab_rows, lane);
-    const int s2 = choose_split_warp(tiles_total * kMT2, kMaxSplit2, a.ctas, n_sel_pad, a.slab_rows, lane);
+    const int s1 = choose_split_warp(tiles_total * kMT1, kMaxSplit1, a.ctas, n_sel_pad, a.slab_rows, lane, kKB1, a.kps1);
+    const int s2 = choose_split_warp(tiles_total * kMT2, kMaxSplit2, a.ctas, n_sel_pad, a.slab_rows, lane, kKB2, a.kps2);
     if (lane == 31) {
-      s_offs[0] = 0;
       sc->offs[0] = 0;
       sc->tile_prefix[0] = 0;
       sc->status = (n_sel > a.rows_cap) ? kErrSchedOverflow : 0;

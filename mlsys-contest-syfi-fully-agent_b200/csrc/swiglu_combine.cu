@@ -15,23 +15,14 @@
 //   references/moe.py:168-200; replaces the fp32 atomics of the reference GEMM2
 //   epilogue and fin_cast8_kernel (moe.cu:2404-2430, 2473-2496).  Tokens without a
 //   local expert get zeros, so the output needs no memset.
-#include <cuda_fp8.h>
-
+#include "epilogue_device.cuh"
 #include "kernels.h"
 
 namespace moe {
 
 namespace {
 
-__device__ __forceinline__ uint8_t to_e4m3(float x) {
-  return static_cast<uint8_t>(__nv_cvt_float_to_fp8(x, __NV_SATFINITE, __NV_E4M3));
-}
-__device__ __forceinline__ float from_e4m3(uint8_t b) {
-  const __half_raw h = __nv_cvt_fp8_to_halfraw(b, __NV_E4M3);
-  return __half2float(__half(h));
-}
-
-// One warp per (row, 128-column block); lane owns 4 consecutive columns.
+// One warp per (row, 128-column block).
 __global__ void __launch_bounds__(256) swiglu_split_kernel(SwigluArgs a) {
   griddep_launch_dependents();
   griddep_wait();
@@ -41,57 +32,9 @@ __global__ void __launch_bounds__(256) swiglu_split_kernel(SwigluArgs a) {
   const int lane = threadIdx.x & 31;
   const long long nblk = static_cast<long long>(n_sel) * kKB2;
   const long long wstride = static_cast<long long>(gridDim.x) * (blockDim.x >> 5);
-  for (long long b = blockIdx.x * static_cast<long long>(blockDim.x >> 5) + (threadIdx.x >> 5); b < nblk; b += wstride) {
-    const int row = static_cast<int>(b / kKB2), kb = static_cast<int>(b % kKB2);
-    const float* p = a.g1 + static_cast<size_t>(row) * k2I + kb * kBlock + lane * 4;
-    float4 x1 = make_float4(0.f, 0.f, 0.f, 0.f), x2 = x1;
-    for (int s = 0; s < split; ++s) {
-      const float4 u = *reinterpret_cast<const float4*>(p + s * slab);
-      const float4 v = *reinterpret_cast<const float4*>(p + s * slab + kI);
-      x1.x += u.x; x1.y += u.y; x1.z += u.z; x1.w += u.w;
-      x2.x += v.x; x2.y += v.y; x2.z += v.z; x2.w += v.w;
-    }
-    float c[4];
-    c[0] = __fmul_rn(x2.x / (1.0f + expf(-x2.x)), x1.x);
-    c[1] = __fmul_rn(x2.y / (1.0f + expf(-x2.y)), x1.y);
-    c[2] = __fmul_rn(x2.z / (1.0f + expf(-x2.z)), x1.z);
-    c[3] = __fmul_rn(x2.w / (1.0f + expf(-x2.w)), x1.w);
-    float amax = fmaxf(fmaxf(fabsf(c[0]), fabsf(c[1])), fmaxf(fabsf(c[2]), fabsf(c[3])));
-#pragma unroll
-    for (int d = 16; d > 0; d >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, d));
-    // power-of-two scale with amax / scale in (224, 448]
-    int e = 0;
-    if (amax > 0.0f && amax < 3.0e38f) {
-      e = ilogbf(amax * (1.0f / 448.0f)) + 1;
-      e = max(-100, min(100, e));
-    }
-    const float scale = scalbnf(1.0f, e), inv = scalbnf(1.0f, -e);
-    uint32_t packed[kNTerms];
-#pragma unroll
-    for (int t = 0; t < kNTerms; ++t) packed[t] = 0;
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      float r = c[i] * inv;
-      if (!(fabsf(r) <= 448.0f)) r = r > 0.0f ? 448.0f : (r < 0.0f ? -448.0f : 0.0f);   // inf / nan guard
-#pragma unroll
-      for (int t = 0; t < kNTerms; ++t) {
-        const uint8_t q = to_e4m3(r);
-        r -= from_e4m3(q);
-        packed[t] |= static_cast<uint32_t>(q) << (8 * i);
-      }
-    }
-#pragma unroll
-    for (int t = 0; t < kNTerms; ++t)
-      *reinterpret_cast<uint32_t*>(a.cq + (static_cast<size_t>(t) * a.rows_cap + row) * kI + kb * kBlock + lane * 4) =
-          packed[t];
-    if (lane == 0) a.c_scale[static_cast<size_t>(row) * kKB2 + kb] = scale;
-  }
-}
-
-__device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
-  uint32_t r;
-  asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
-  return r;
+  for (long long b = blockIdx.x * static_cast<long long>(blockDim.x >> 5) + (threadIdx.x >> 5); b < nblk; b += wstride)
+    swiglu_split_unit(a.g1, slab, split, static_cast<int>(b / kKB2), static_cast<int>(b % kKB2), lane, a.cq,
+                      a.c_scale, a.rows_cap);
 }
 
 // One thread per 4 output columns of a token.
@@ -106,27 +49,8 @@ __global__ void __launch_bounds__(256) combine_kernel(CombineArgs a) {
   for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
        i += static_cast<long long>(gridDim.x) * blockDim.x) {
     const int t = static_cast<int>(i / kVec), c = static_cast<int>(i % kVec);
-    const int n = __popc(a.local_mask[t]);
-    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-    for (int j = 0; j < n; ++j) {
-      const int row = a.tok_rows[t * kTopK + j];
-      const float w = a.perm_weight[row];
-      const float* p = a.o + static_cast<size_t>(row) * kH + c * 4;
-      float4 v = *reinterpret_cast<const float4*>(p);
-      for (int s = 1; s < split; ++s) {
-        const float4 u = *reinterpret_cast<const float4*>(p + s * slab);
-        v.x += u.x; v.y += u.y; v.z += u.z; v.w += u.w;
-      }
-      // multiply, then add, each rounded (no FMA contraction): the definition's index_add_(O * w)
-      acc.x = __fadd_rn(acc.x, __fmul_rn(v.x, w));
-      acc.y = __fadd_rn(acc.y, __fmul_rn(v.y, w));
-      acc.z = __fadd_rn(acc.z, __fmul_rn(v.z, w));
-      acc.w = __fadd_rn(acc.w, __fmul_rn(v.w, w));
-    }
-    uint2 o;
-    o.x = pack_bf16x2(acc.x, acc.y);
-    o.y = pack_bf16x2(acc.z, acc.w);
-    *reinterpret_cast<uint2*>(a.out_bf16 + static_cast<size_t>(t) * kH + c * 4) = o;
+    combine_unit(a.o, slab, split, __popc(a.local_mask[t]), a.tok_rows + t * kTopK, a.perm_weight, c,
+                 a.out_bf16 + static_cast<size_t>(t) * kH);
   }
 }
 

@@ -215,3 +215,20 @@ def test_fp8_umma_accumulation_known_answer(pkg, dev, W):
     got = im["g1"][rows].double()
     scale = float(w.abs().sum(dim=(2, 3)).max())
     assert float((got - want[None, :]).abs().max()) <= 2e-6 * scale
+
+
+def test_tvm_ffi_entry_point_matches_c_abi(pkg, dev, W):
+    """The harness-facing export `run` (tvm-ffi, the reference's binding) gives the same bits as the C ABI."""
+    tvm_ffi = pytest.importorskip("tvm_ffi")
+    lib = pkg.build.build_tvmffi()
+    if lib is None:
+        pytest.skip("tvm-ffi shim not built")
+    mod = tvm_ffi.load_module(lib)
+    for T, seed in ((8, 0), (130, 4)):
+        tok = pkg.gen.make_tokens(T, seed, dev)
+        want = run_op(pkg, tok, W, 32).clone()
+        out = torch.zeros(T, 7168, dtype=torch.bfloat16, device=dev)
+        mod.run(tok.routing_logits, tok.routing_bias, tok.hidden_states, tok.hidden_states_scale,
+                W.gemm1_weights, W.gemm1_weights_scale, W.gemm2_weights, W.gemm2_weights_scale, 32, RSF, out)
+        torch.cuda.synchronize()
+        assert torch.equal(out.view(torch.int16), want.view(torch.int16))
