@@ -9,9 +9,12 @@ is quoted on); N > 1 (under torchrun) measures the 256-expert layer with expert
 parallelism over N GPUs (T = 16384 tokens, NCCL all-to-all dispatch and combine).
 Rank 0 prints ONE JSON line.
 
-Timing: CUDA events on the launching stream around every step, L2 flushed
-between steps by writing a 512 MB buffer (a decode step touches < 126 MB, so
-without the flush its weights would be served from L2), max over ranks.
+Timing: CUDA events on the launching stream around the K timed steps (W warm-up
+steps before), max over ranks.  A decode step touches < 126 MB of weights, so
+consecutive steps rotate through R replicas of the shard's weights (different
+addresses, same values) chosen so that a replica is reused only after more
+than 3x the L2 capacity has been streamed: every step reads its weights from HBM
+("inputs larger than L2"), without a flush kernel leaving dirty lines behind.
 """
 from __future__ import annotations
 
@@ -47,7 +50,9 @@ WORKLOADS = {
 
 # dram__bytes_read.sum + dram__bytes_write.sum of one GEMM1 launch, from the ncu capture
 # summarised in profiles/ (None until a capture of that workload exists).
-NCU_TRAFFIC_BYTES = {}
+NCU_TRAFFIC_BYTES = {"decode_t1": 58_821_120 + 176_896,        # profiles/grouped_gemm_fused_decode_t1.md
+                     "skew_t64": 474_010_000 + 12_660_000,     # profiles/launch_shares_skew_t64_prefill_t4096.md
+                     "prefill_t4096": 808_470_000 + 67_240_000}
 
 W13_BYTES = 4096 * 7168 + 32 * 56 * 4          # one expert's GEMM1 weights + scales
 W2_BYTES = 7168 * 2048 + 56 * 16 * 4
@@ -124,19 +129,37 @@ def algorithmic_bytes(T, n_sel, n_active, n_tokens_with_local):
     return (n_active * (W13_BYTES + W2_BYTES) + n_tokens_with_local * ROW_BYTES + T * 1024 + T * 7168 * 2)
 
 
-def time_steps(fn, steps, warmup, flush):
-    for _ in range(warmup):
-        flush.zero_()
-        fn()
+def time_steps(fn, steps, warmup):
+    """W warm-up calls, then exactly K calls between two events; returns ms per step."""
+    for i in range(warmup):
+        fn(i)
     torch.cuda.synchronize()
-    evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(steps)]
-    for e0, e1 in evs:
-        flush.zero_()
-        e0.record()
-        fn()
-        e1.record()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(steps):
+        fn(warmup + i)
+    e1.record()
     torch.cuda.synchronize()
-    return [e0.elapsed_time(e1) for e0, e1 in evs]
+    return e0.elapsed_time(e1) / steps
+
+
+L2_BYTES = 126 << 20
+
+
+def weight_replicas(W, touched_bytes):
+    """Enough copies of the shard's weights that a copy is reused after > 3 x L2 of other traffic."""
+    n = 1
+    while n < 8 and touched_bytes * (n - 1) < 3 * L2_BYTES:
+        n += 1
+    reps = [W]
+    for _ in range(n - 1):
+        reps.append(type(W)(W.gemm1_weights.clone(), W.gemm1_weights_scale.clone(), W.gemm2_weights.clone(),
+                            W.gemm2_weights_scale.clone()))
+    return reps
+
+
+def wtuple(w):
+    return (w.gemm1_weights, w.gemm1_weights_scale, w.gemm2_weights, w.gemm2_weights_scale)
 
 
 def bench_single(args):
@@ -150,33 +173,37 @@ def bench_single(args):
     W = gen.make_shard_weights(0, dev)
     tok = gen.make_tokens(T, wl["token_seed"], dev, wl["skew"])
     out = torch.empty(T, 7168, dtype=torch.bfloat16, device=dev)
-    flush = torch.empty(512 << 20, dtype=torch.uint8, device=dev)
-    wargs = (W.gemm1_weights, W.gemm1_weights_scale, W.gemm2_weights, W.gemm2_weights_scale)
+    wargs = wtuple(W)
+    # one untimed call tells how many experts the batch touches, which sizes the replica ring
+    op.run(tok.routing_logits, tok.routing_bias, tok.hidden_states, tok.hidden_states_scale, *wargs, 0, RSF, out)
+    sched = op.intermediates(T)["sched"]
+    reps = weight_replicas(W, max(1, sched.n_active) * (W13_BYTES + W2_BYTES))
+    R = len(reps)
 
-    def step():
-        op.run(tok.routing_logits, tok.routing_bias, tok.hidden_states, tok.hidden_states_scale, *wargs, 0, RSF, out)
+    def step(i=0):
+        op.run(tok.routing_logits, tok.routing_bias, tok.hidden_states, tok.hidden_states_scale,
+               *wtuple(reps[i % R]), 0, RSF, out)
 
     # ---- device-resident inputs: `value`
     launches0 = loader.launch_count()
     with ClockSampler(0) as clocks:
-        ms = time_steps(step, args.steps, args.warmup, flush)
+        ms_step = time_steps(step, args.steps, args.warmup)
     launches = (loader.launch_count() - launches0) * args.steps // (args.steps + args.warmup)
     assert op.kernel_status() == 0
     im = op.intermediates(T)
     sched = im["sched"]
-    total_s = sum(ms) / 1e3
-    value = args.steps * T / total_s
+    value = T / (ms_step * 1e-3)
 
     # ---- host buffers through the host entry point: `e2e`
     pin = lambda t: t.cpu().pin_memory()
     h = [pin(tok.routing_logits), pin(tok.routing_bias), pin(tok.hidden_states), pin(tok.hidden_states_scale)]
     out_h = torch.empty(T, 7168, dtype=torch.bfloat16).pin_memory()
 
-    def step_host():
-        op.run_host(*h, *wargs, 0, RSF, out_h)
+    def step_host(i=0):
+        op.run_host(*h, *wtuple(reps[i % R]), 0, RSF, out_h)
 
-    ms_host = time_steps(step_host, args.steps, args.warmup, flush)
-    e2e_value = args.steps * T / (sum(ms_host) / 1e3)
+    ms_host = time_steps(step_host, args.steps, args.warmup)
+    e2e_value = T / (ms_host * 1e-3)
     h2d = sum(t.numel() * t.element_size() for t in h)
     d2h = out_h.numel() * out_h.element_size()
 
@@ -185,14 +212,14 @@ def bench_single(args):
     acc = {}
     nprof = max(10, min(args.steps, 100))
     for i in range(nprof + 3):
-        flush.zero_()
-        step()
+        step(i)
         st = loader.stage_times_ms()
         if i >= 3:
             for k, v in st.items():
                 acc[k] = acc.get(k, 0.0) + v
     loader.set_profiling(False)
     stage_us = {k: v / nprof * 1e3 for k, v in acc.items()}
+    fused = T <= 16
     dominant = max(("gemm1", "gemm2"), key=lambda k: stage_us[k])
     wbytes = W13_BYTES if dominant == "gemm1" else W2_BYTES
     rbytes = ROW_BYTES if dominant == "gemm1" else 0
@@ -201,6 +228,8 @@ def bench_single(args):
     achieved = kernel_bytes / (stage_us[dominant] * 1e-6) / 1e9
     n_local_tokens = int((im["local_mask"] != 0).sum())
     op_bytes = algorithmic_bytes(T, sched.n_sel, sched.n_active, n_local_tokens)
+    step(0)       # leave `out` holding replica 0's result for the self-check below
+    torch.cuda.synchronize()
 
     # ---- self-check against the oracle and the CPU baseline (bounded sample of the same workload)
     sys.path.insert(0, os.path.join(ROOT, "oracle"))
@@ -221,23 +250,28 @@ def bench_single(args):
 
     line = {
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
-        "ms_per_step": sum(ms) / len(ms), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "fp8_e4m3", "data": "synthetic",
         "config": {"workload": name, "T": T, "token_seed": wl["token_seed"], "weight_seed": 0,
                    "routing_skew": wl["skew"], "local_expert_offset": 0, "n_sel": sched.n_sel,
-                   "active_experts": sched.n_active, "l2": "flushed between steps (512 MB write)",
+                   "active_experts": sched.n_active,
+                   "l2": f"{R} weight replicas rotated: {R * sched.n_active * (W13_BYTES + W2_BYTES) >> 20} MiB "
+                         "streamed per cycle > 3 x 126 MB L2",
                    "split_k": [sched.split1, sched.split2], "token_tile": sched.n_tile},
         "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-                "ms_per_step": sum(ms_host) / len(ms_host),
+                "ms_per_step": ms_host,
                 "note": "token tensors from pinned host memory, bf16 output read back; weights stay resident"},
         "gpu_launches": int(launches),
         "clocks": clocks.summary(),
-        "roofline": {"bound": "hbm", "kernel": f"grouped_gemm_kernel<{1 if dominant == 'gemm1' else 2},{sched.n_tile}>",
+        "roofline": {"bound": "hbm",
+                     "kernel": f"grouped_gemm_kernel<{1 if dominant == 'gemm1' else 2},{sched.n_tile}"
+                               + (",fused>: in-kernel routing + GEMM + " + ("SwiGLU" if dominant == "gemm1" else "combine")
+                                  + " tail" if fused else ">"),
                      "achieved": achieved, "peak": peak, "peak_kind": peak_kind, "unit": "GB/s",
                      "frac": achieved / peak, "traffic": NCU_TRAFFIC_BYTES.get(name),
                      "algorithmic_bytes_per_launch": kernel_bytes, "launch_us": stage_us[dominant],
-                     "whole_op": {"algorithmic_bytes": op_bytes, "achieved": op_bytes / (sum(ms) / len(ms) * 1e-3) / 1e9,
-                                  "frac": op_bytes / (sum(ms) / len(ms) * 1e-3) / 1e9 / peak}},
+                     "whole_op": {"algorithmic_bytes": op_bytes, "achieved": op_bytes / (ms_step * 1e-3) / 1e9,
+                                  "frac": op_bytes / (ms_step * 1e-3) / 1e9 / peak}},
         "stage_us": stage_us,
         "cpu_baseline": {"value": calls * T / cpu_s, "unit": UNIT, "cores": torch.get_num_threads(), "kind": "port",
                          "sample": f"{calls} calls of the oracle port on the same T={T} batch ({cpu_s:.1f} s); "
@@ -245,43 +279,45 @@ def bench_single(args):
         "parity": {k: m[k] for k in ("max_abs_over_rms", "cosine", "n_diff", "n_one_step")},
     }
     if args.sweep:
-        line["sweep"] = sweep(pkg, W, flush, [n for n in WORKLOADS if n != name], peak)
+        line["sweep"] = sweep(pkg, W, [n for n in WORKLOADS if n != name], peak)
     print(json.dumps(line))
 
 
-def sweep(pkg, W, flush, names, peak):
+def sweep(pkg, W, names, peak):
     """Tokens/s and per-kernel roofline fractions of the other single-GPU workloads."""
     gen, op, loader = pkg.gen, pkg.op, pkg.loader
     dev = W.gemm1_weights.device
-    wargs = (W.gemm1_weights, W.gemm1_weights_scale, W.gemm2_weights, W.gemm2_weights_scale)
     rows = []
     for name in names:
         wl = WORKLOADS[name]
         T = wl["T"]
         tok = gen.make_tokens(T, wl["token_seed"], dev, wl["skew"])
         out = torch.empty(T, 7168, dtype=torch.bfloat16, device=dev)
+        op.run(tok.routing_logits, tok.routing_bias, tok.hidden_states, tok.hidden_states_scale, *wtuple(W), 0, RSF, out)
+        s = op.intermediates(T)["sched"]
+        reps = weight_replicas(W, max(1, s.n_active) * (W13_BYTES + W2_BYTES))
+        R = len(reps)
 
-        def step():
-            op.run(tok.routing_logits, tok.routing_bias, tok.hidden_states, tok.hidden_states_scale, *wargs, 0, RSF,
-                   out)
-        ms = time_steps(step, 20, 3, flush)
+        def step(i=0):
+            op.run(tok.routing_logits, tok.routing_bias, tok.hidden_states, tok.hidden_states_scale,
+                   *wtuple(reps[i % R]), 0, RSF, out)
+        ms = time_steps(step, 30, 5)
         loader.set_profiling(True)
         acc = {}
-        for _ in range(10):
-            flush.zero_()
-            step()
+        for i in range(10):
+            step(i)
             for k, v in loader.stage_times_ms().items():
                 acc[k] = acc.get(k, 0.0) + v * 100.0
         loader.set_profiling(False)
-        s = op.intermediates(T)["sched"]
-        us = sum(ms) / len(ms) * 1e3
-        rows.append({"workload": name, "T": T, "n_sel": s.n_sel, "active_experts": s.n_active,
+        us = ms * 1e3
+        rows.append({"workload": name, "T": T, "n_sel": s.n_sel, "active_experts": s.n_active, "replicas": R,
                      "us_per_step": us, "tokens_per_s": T / us * 1e6,
                      "gemm1_gbs": (s.n_active * W13_BYTES + s.n_sel * ROW_BYTES) / acc["gemm1"] / 1e3,
                      "gemm2_gbs": s.n_active * W2_BYTES / acc["gemm2"] / 1e3,
                      "whole_op_hbm_frac": s.n_active * (W13_BYTES + W2_BYTES) / us / 1e3 / peak,
                      "fp8_tflops": s.n_sel * 88080384 / us / 1e6,
                      "stage_us": acc})
+        del reps
     return rows
 
 

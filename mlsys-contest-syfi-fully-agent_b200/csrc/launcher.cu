@@ -323,7 +323,7 @@ extern "C" int moe_fp8_block_scale_run(const float* routing_logits, const uint16
   stage_mark(0, stream);
   launch_route_permute(ra, pa, stream);
   MOE_CUDA(cudaGetLastError());
-  g_launches += T <= 256 ? 1 : 2;
+  g_launches += T <= 32 ? 1 : 2;
   stage_mark(1, stream);
 
   GatherArgs ga{sched, perm_token, hidden_states, hidden_states_scale, T, a_packed, a_scale_rows};

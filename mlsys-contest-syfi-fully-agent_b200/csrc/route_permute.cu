@@ -209,7 +209,7 @@ __global__ void __launch_bounds__(256) gather_rows_kernel(GatherArgs a) {
 }
 
 void launch_route_permute(const RouteArgs& r, const PermuteArgs& p, cudaStream_t stream) {
-  if (r.T <= 256) {
+  if (r.T <= 32) {
     launch_pdl(route_permute_kernel, dim3(1), dim3(1024), 0, stream, r, p);
   } else {
     const int grid = (r.T + 7) / 8 < 4 * kNumSMs ? (r.T + 7) / 8 : 4 * kNumSMs;
