@@ -65,18 +65,17 @@ struct Cfg {
   static constexpr int MMA_PER_K4 = STACK ? 1 : NTERMS;
   static constexpr int PLANES = STACK ? NTERMS : 1;                     // column planes the epilogue sums
   static constexpr int KB_COLS = N_MMA;                                 // TMEM columns of one K-block partial
-  static constexpr int G = KB_COLS <= 16 ? 4 : KB_COLS <= 64 ? 2 : 1;   // K-blocks per hand-off
-  static constexpr int NBUF_FIT = 512 / (G * KB_COLS);
-  static constexpr int NBUF = NBUF_FIT > 4 ? 4 : NBUF_FIT;
-  static constexpr int TMEM_USED = NBUF * G * KB_COLS;
-  static constexpr int TMEM_COLS = TMEM_USED <= 32 ? 32 : TMEM_USED <= 64 ? 64 : TMEM_USED <= 128 ? 128
-                                   : TMEM_USED <= 256 ? 256 : 512;
-  static constexpr int CPW = N_TILE / 2;                                // token columns per epilogue warp
   static constexpr int A_BYTES = 128 * 128;
   static constexpr int B_BYTES = N_TILE * 128;
   static constexpr int KB_BYTES = A_BYTES + NTERMS * B_BYTES;           // operands of one K-block
-  static constexpr int KPS = KB_BYTES <= 24 * 1024 ? 2 : 1;             // K-blocks per pipeline stage (one TMA each
-                                                                        // for the weights and the tokens per stage)
+  // K-blocks per pipeline stage.  A stage is also the TMEM hand-off unit: ONE tcgen05.commit per
+  // stage tells the producer that the stage's shared memory is free and the promotion warps that
+  // its partial sums are in TMEM.  (A commit costs the tensor pipe roughly 400 cycles, about as
+  // much as six UMMAs of a 128-token tile, so two K-blocks share one wherever shared memory and
+  // TMEM allow two stages of two.)
+  static constexpr int KPS = (2 * KB_BYTES <= 64 * 1024 && 2 * KB_COLS <= 256) ? 2 : 1;
+  static constexpr int G = KPS;
+  static constexpr int CPW = N_TILE / 2;                                // token columns per epilogue warp
   static constexpr int STAGE_BYTES = KPS * KB_BYTES;
   static constexpr int SC_BUFS = N_TILE <= 32 ? 2 : 1;                  // scale-product tables
   static constexpr int SC_BYTES = SC_BUFS * KB * N_TILE * 4;
@@ -85,18 +84,26 @@ struct Cfg {
   static constexpr int STAGES_FIT = (BUDGET - SC_BYTES - AUX_BYTES) / STAGE_BYTES;
   static constexpr int STAGES = STAGES_FIT > 10 ? 10 : STAGES_FIT;
   static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + SC_BYTES + AUX_BYTES + 1024;
+  static constexpr int NBUF_FIT = 512 / (G * KB_COLS);
+  // TMEM buffers (one stage of partials each).  Not more than shared-memory stages: the promotion warps
+  // and the producer wait on the same per-stage barrier, and a stage must not complete a second phase
+  // before the promotion warps have seen the first; the issuer is at most NBUF stages ahead of them.
+  static constexpr int NBUF_CAP = NBUF_FIT > 4 ? 4 : NBUF_FIT;
+  static constexpr int NBUF = NBUF_CAP > STAGES ? STAGES : NBUF_CAP;
+  static constexpr int TMEM_USED = NBUF * G * KB_COLS;
+  static constexpr int TMEM_COLS = TMEM_USED <= 32 ? 32 : TMEM_USED <= 64 ? 64 : TMEM_USED <= 128 ? 128
+                                   : TMEM_USED <= 256 ? 256 : 512;
   static_assert(STAGES >= 2, "ring too small");
-  static_assert(KB % KPS == 0, "K-blocks per stage must divide the K extent");
-  static_assert(NBUF >= 2 && TMEM_USED <= 512, "TMEM budget");
+  static_assert(KB % KPS == 0 && (KPS & (KPS - 1)) == 0, "K-blocks per stage: a power of two dividing the K extent");
+  static_assert(NBUF >= 2 && NBUF <= STAGES && TMEM_USED <= 512, "TMEM budget / ring depths");
   static_assert(N_MMA % 16 == 0 && N_MMA >= 16 && N_MMA <= 256, "invalid UMMA N for M = 128");
   static_assert(SMEM_BYTES > 116 * 1024, "one CTA per SM is assumed (TMEM is allocated without contention)");
 };
 
 struct Aux {
-  uint64_t full[10];
-  uint64_t empty[10];
-  uint64_t tfull[4];
-  uint64_t tempty[4];
+  uint64_t full[10];       // TMA -> issuer: the stage's operands have landed
+  uint64_t done[10];       // issuer -> producer and promotion warps: the stage's UMMAs have completed
+  uint64_t tempty[4];      // promotion warps -> issuer: the TMEM buffer has been read
   uint64_t esync;          // bounded replacement for a named barrier among the epilogue threads
   uint32_t tmem_base;
   int abort;
@@ -207,12 +214,9 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
     aux->abort = 0;
     for (int s = 0; s < C::STAGES; ++s) {
       mbar_init(smem_u32(&aux->full[s]), 1);
-      mbar_init(smem_u32(&aux->empty[s]), 1);
+      mbar_init(smem_u32(&aux->done[s]), 1);
     }
-    for (int b = 0; b < C::NBUF; ++b) {
-      mbar_init(smem_u32(&aux->tfull[b]), 1);
-      mbar_init(smem_u32(&aux->tempty[b]), kEpiWarps);
-    }
+    for (int b = 0; b < C::NBUF; ++b) mbar_init(smem_u32(&aux->tempty[b]), kEpiWarps);
     mbar_init(smem_u32(&aux->esync), kEpiWarps * 32);
     fence_mbar_init();
     tma_prefetch_desc(&tm_w);
@@ -346,64 +350,64 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
     if (lane == 0) {
-      uint32_t it = 0;
+      const uint32_t smem_base = smem_u32(smem);
+      const uint32_t full_base = smem_u32(&aux->full[0]), done_base = smem_u32(&aux->done[0]);
+      uint32_t stage = 0, ph = 0;
       bool ok = true;
       for (int i = blockIdx.x; ok && i < items; i += gridDim.x) {
         const Item w = decode_item<GEMM, N_TILE>(i, split, aux);
         const int wy = w.e * C::M_TOTAL + w.m * 128;
-        for (int kb = w.kb0; kb < w.kb1; kb += C::KPS, ++it) {
-          const uint32_t stage = it % C::STAGES, ph = (it / C::STAGES) & 1u;
-          if (!mbar_wait(smem_u32(&aux->empty[stage]), ph ^ 1u, abort_flag)) { ok = false; break; }
-          TRACE(0, it);
-          const uint32_t bar = smem_u32(&aux->full[stage]);
+        const int by = (FUSED && GEMM == 1) ? 0 : w.row0;
+        for (int kb = w.kb0; kb < w.kb1; kb += C::KPS) {
+          if (!mbar_wait(done_base + stage * 8, ph ^ 1u, abort_flag)) { ok = false; break; }
+          const uint32_t bar = full_base + stage * 8;
           mbar_arrive_expect_tx(bar, C::STAGE_BYTES);
-          const uint32_t dst = smem_u32(smem + stage * C::STAGE_BYTES);
+          const uint32_t dst = smem_base + stage * C::STAGE_BYTES;
           // weights: [KPS][128 rows][128 B]; tokens: [KPS][NTERMS planes][N_TILE rows][128 B]
           tma_load_3d(dst, &tm_w, 0, wy, kb, bar);
-          if (GEMM == 1) tma_load_3d(dst + C::KPS * C::A_BYTES, &tm_b, 0, FUSED ? 0 : w.row0, kb, bar);
-          else tma_load_4d(dst + C::KPS * C::A_BYTES, &tm_b, 0, w.row0, 0, kb, bar);
+          if (GEMM == 1) tma_load_3d(dst + C::KPS * C::A_BYTES, &tm_b, 0, by, kb, bar);
+          else tma_load_4d(dst + C::KPS * C::A_BYTES, &tm_b, 0, by, 0, kb, bar);
+          if (++stage == C::STAGES) { stage = 0; ph ^= 1u; }
         }
       }
     }
     __syncwarp();   // block-wide barriers below need whole warps
   } else if (warp == 1) {
     // ------------------------------------------------------------------ UMMA issuer
+    // One thread; its loop is the critical path of the large-tile regimes (every instruction is
+    // dependent-issue latency), so ring positions are kept incrementally and the descriptors are
+    // formed with one add from constants.
     if (lane == 0) {
       constexpr uint32_t idesc = umma_idesc_e4m3(128, C::N_MMA);
-      uint32_t it = 0, gi = 0;
+      const uint64_t desc_const = umma_desc_k_sw128(0);          // everything but the start address
+      const uint32_t smem_base = smem_u32(smem);
+      const uint32_t full_base = smem_u32(&aux->full[0]), done_base = smem_u32(&aux->done[0]);
+      const uint32_t tempty_base = smem_u32(&aux->tempty[0]);
+      uint32_t stage = 0, ph = 0, buf = 0, bph = 0;
       bool ok = true;
       for (int i = blockIdx.x; ok && i < items; i += gridDim.x) {
         const Item w = decode_item<GEMM, N_TILE>(i, split, aux);
-        const int nkb = w.kb1 - w.kb0;
-        for (int kbl = 0; ok && kbl < nkb; kbl += C::G, ++gi) {
-          const uint32_t buf = gi % C::NBUF, bph = (gi / C::NBUF) & 1u;
-          if (!mbar_wait(smem_u32(&aux->tempty[buf]), bph ^ 1u, abort_flag)) { ok = false; break; }
-          const int gsize = min(C::G, nkb - kbl);
-          for (int g = 0; g < gsize; ++g) {
-            const int u = (kbl + g) % C::KPS;          // K-block inside the current stage
-            const uint32_t stage = it % C::STAGES, ph = (it / C::STAGES) & 1u;
-            if (u == 0) {
-              if (!mbar_wait(smem_u32(&aux->full[stage]), ph, abort_flag)) { ok = false; break; }
-              TRACE(1, it);
-              tc_fence_after_sync();
-            }
-            const uint32_t sbase = smem_u32(smem + stage * C::STAGE_BYTES);
-            const uint64_t adesc = umma_desc_k_sw128(sbase + u * C::A_BYTES);
+        for (int kb = w.kb0; kb < w.kb1; kb += C::KPS) {        // items span whole stages
+          if (!mbar_wait(tempty_base + buf * 8, bph ^ 1u, abort_flag)) { ok = false; break; }
+          if (!mbar_wait(full_base + stage * 8, ph, abort_flag)) { ok = false; break; }
+          tc_fence_after_sync();
+          const uint32_t sbase = smem_base + stage * C::STAGE_BYTES;
+#pragma unroll
+          for (int u = 0; u < C::KPS; ++u) {
+            const uint64_t adesc = desc_const | ((sbase + u * C::A_BYTES) >> 4);
             const uint32_t sb = sbase + C::KPS * C::A_BYTES + u * (C::NTERMS * C::B_BYTES);
-            const uint32_t d = tmem_base + buf * (C::G * C::KB_COLS) + g * C::KB_COLS;
+            const uint32_t d = tmem_base + buf * (C::G * C::KB_COLS) + u * C::KB_COLS;
 #pragma unroll
             for (int t = 0; t < C::MMA_PER_K4; ++t) {
-              const uint64_t bdesc = umma_desc_k_sw128(sb + t * C::B_BYTES);
+              const uint64_t bdesc = desc_const | ((sb + t * C::B_BYTES) >> 4);
 #pragma unroll
               for (int k4 = 0; k4 < 4; ++k4)   // +32 bytes of K inside the 128-byte swizzle atom = +2 encoded units
                 umma_f8(d, adesc + 2 * k4, bdesc + 2 * k4, idesc, (t | k4) != 0 ? 1u : 0u);
             }
-            if (u == C::KPS - 1) {               // items span whole stages, so this is also the item's last K-block
-              umma_commit(smem_u32(&aux->empty[stage]));
-              ++it;
-            }
           }
-          if (ok) umma_commit(smem_u32(&aux->tfull[buf]));
+          umma_commit(done_base + stage * 8);
+          if (++stage == C::STAGES) { stage = 0; ph ^= 1u; }
+          if (++buf == C::NBUF) { buf = 0; bph ^= 1u; }
         }
       }
     }
@@ -414,7 +418,9 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
     const int h = (warp - 2) >> 2;                // which half of the token columns
     const int etid = threadIdx.x - 64;            // 0..255
     const uint32_t lane_addr = static_cast<uint32_t>(q * 32) << 16;
-    uint32_t gi = 0, eph = 0, nitem = 0;
+    uint32_t eph = 0, nitem = 0;
+    uint32_t stage = 0, ph = 0, buf = 0, bph = 0;      // same ring positions as the issuer
+    const uint32_t done_base = smem_u32(&aux->done[0]), tempty_base = smem_u32(&aux->tempty[0]);
     bool ok = true;
     // all epilogue threads meet here; bounded like every other wait in this kernel
     auto epi_sync = [&]() {
@@ -472,45 +478,42 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
 #pragma unroll
       for (int j = 0; j < C::CPW; ++j) acc[j] = 0.0f;
 
-      for (int kbl = 0; kbl < nkb; kbl += C::G, ++gi) {
-        const uint32_t buf = gi % C::NBUF, bph = (gi / C::NBUF) & 1u;
-        const int gsize = min(C::G, nkb - kbl);
-        if (!mbar_wait(smem_u32(&aux->tfull[buf]), bph, abort_flag)) { ok = false; break; }
-        if (etid == 0) TRACE(2, 8 + gi);
+      for (int kbl = 0; kbl < nkb; kbl += C::G) {
+        if (!mbar_wait(done_base + stage * 8, ph, abort_flag)) { ok = false; break; }
         tc_fence_after_sync();
         const uint32_t taddr = tmem_base + lane_addr + buf * (C::G * C::KB_COLS) + h * C::CPW;
-        float v[C::G][C::PLANES][C::CPW];
 #pragma unroll
-        for (int g = 0; g < C::G; ++g)
-          if (g < gsize) {
+        for (int g = 0; g < C::G; ++g) {
+          // one K-block's partial at a time (register budget); the buffer is released after the last read
+          float v[C::PLANES][C::CPW];
 #pragma unroll
-            for (int p = 0; p < C::PLANES; ++p) tmem_ld_cols<C::CPW>(taddr + g * C::KB_COLS + p * N_TILE, v[g][p]);
+          for (int p = 0; p < C::PLANES; ++p) tmem_ld_cols<C::CPW>(taddr + g * C::KB_COLS + p * N_TILE, v[p]);
+          tmem_wait_ld();
+          if (g == C::G - 1) {
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(tempty_base + buf * 8);
           }
-        tmem_wait_ld();
-        tc_fence_before_sync();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(smem_u32(&aux->tempty[buf]));   // partials are in registers: free the buffer
+          const float4* scv = reinterpret_cast<const float4*>(sc + (kbl + g) * N_TILE + h * C::CPW);
 #pragma unroll
-        for (int g = 0; g < C::G; ++g)
-          if (g < gsize) {
-            const float4* scv = reinterpret_cast<const float4*>(sc + (kbl + g) * N_TILE + h * C::CPW);
+          for (int u = 0; u < C::CPW / 4; ++u) {
+            const float4 f = scv[u];
+            float s4[4];
 #pragma unroll
-            for (int u = 0; u < C::CPW / 4; ++u) {
-              const float4 f = scv[u];
-              float s4[4];
+            for (int x = 0; x < 4; ++x) {
+              float sum = v[C::PLANES - 1][u * 4 + x];
 #pragma unroll
-              for (int x = 0; x < 4; ++x) {
-                float s = v[g][C::PLANES - 1][u * 4 + x];
-#pragma unroll
-                for (int p = C::PLANES - 2; p >= 0; --p) s += v[g][p][u * 4 + x];   // smallest terms first
-                s4[x] = s;
-              }
-              acc[u * 4 + 0] = fmaf(s4[0], f.x, acc[u * 4 + 0]);
-              acc[u * 4 + 1] = fmaf(s4[1], f.y, acc[u * 4 + 1]);
-              acc[u * 4 + 2] = fmaf(s4[2], f.z, acc[u * 4 + 2]);
-              acc[u * 4 + 3] = fmaf(s4[3], f.w, acc[u * 4 + 3]);
+              for (int p = C::PLANES - 2; p >= 0; --p) sum += v[p][u * 4 + x];   // smallest terms first
+              s4[x] = sum;
             }
+            acc[u * 4 + 0] = fmaf(s4[0], f.x, acc[u * 4 + 0]);
+            acc[u * 4 + 1] = fmaf(s4[1], f.y, acc[u * 4 + 1]);
+            acc[u * 4 + 2] = fmaf(s4[2], f.z, acc[u * 4 + 2]);
+            acc[u * 4 + 3] = fmaf(s4[3], f.w, acc[u * 4 + 3]);
           }
+        }
+        if (++stage == C::STAGES) { stage = 0; ph ^= 1u; }
+        if (++buf == C::NBUF) { buf = 0; bph ^= 1u; }
       }
       if (!ok) break;
       if constexpr (FUSED && GEMM == 1) {      // token columns -> the expert's rows (ascending token)

@@ -23,7 +23,7 @@ constexpr int kKB1 = kH / kBlock;        // 56 K-blocks in GEMM1
 constexpr int kKB2 = kI / kBlock;        // 16 K-blocks in GEMM2
 constexpr int kMT1 = k2I / kBlock;       // 32 weight-row tiles per expert in GEMM1
 constexpr int kMT2 = kH / kBlock;        // 56 weight-row tiles per expert in GEMM2
-constexpr int kNTerms = 4;               // e4m3 terms the SwiGLU output is split into for GEMM2
+constexpr int kNTerms = 3;               // e4m3 terms the SwiGLU output is split into for GEMM2
 constexpr int kMaxSplit1 = 14;           // split-K limits (>= 4 K-blocks per split)
 constexpr int kMaxSplit2 = 8;
 constexpr int kMinSlabRows = 2048;       // slab capacity floor so that small batches can split K

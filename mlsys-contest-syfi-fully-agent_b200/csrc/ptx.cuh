@@ -155,14 +155,12 @@ __device__ __forceinline__ void tc_fence_after_sync() {
 // inner extent produces): 8-row groups are 1024 bytes apart (SBO), the leading
 // offset is unused for swizzled K-major layouts, descriptor version 1 (sm_100),
 // layout type 2 (SWIZZLE_128B).
-__device__ __forceinline__ uint64_t umma_desc_k_sw128(uint32_t smem_addr) {
-  uint64_t d = 0;
-  d |= static_cast<uint64_t>((smem_addr & 0x3FFFFu) >> 4);        // start address, bits [0,14)
-  d |= static_cast<uint64_t>(1) << 16;                            // leading byte offset (ignored), bits [16,30)
-  d |= static_cast<uint64_t>(1024 >> 4) << 32;                    // stride byte offset, bits [32,46)
-  d |= static_cast<uint64_t>(1) << 46;                            // version = 1, bits [46,48)
-  d |= static_cast<uint64_t>(2) << 61;                            // SWIZZLE_128B, bits [61,64)
-  return d;
+__host__ __device__ constexpr uint64_t umma_desc_k_sw128(uint32_t smem_addr) {
+  return static_cast<uint64_t>((smem_addr & 0x3FFFFu) >> 4)        // start address, bits [0,14)
+         | (static_cast<uint64_t>(1) << 16)                         // leading byte offset (ignored), bits [16,30)
+         | (static_cast<uint64_t>(1024 >> 4) << 32)                 // stride byte offset, bits [32,46)
+         | (static_cast<uint64_t>(1) << 46)                         // version = 1, bits [46,48)
+         | (static_cast<uint64_t>(2) << 61);                        // SWIZZLE_128B, bits [61,64)
 }
 
 // Instruction descriptor for kind::f8f6f4, A and B both e4m3 and K-major, fp32 accumulate.

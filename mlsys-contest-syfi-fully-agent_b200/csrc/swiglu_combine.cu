@@ -7,9 +7,13 @@
 //   and writes C as kNTerms e4m3 planes with one power-of-two scale per (row, 128 block):
 //       C ~= scale * (t0 + t1 + ... ),  t_i = e4m3(residual after t_0..t_{i-1})
 //   All planes share the scale, so GEMM2 accumulates the kNTerms products of a K-block
-//   in the same TMEM accumulator.  Four terms carry ~16 significant bits of C, the
-//   same as the bf16 hi+lo pair the reference kernel uses (moe.cu:1241-1251), which is
-//   what the output tolerance needs; a single e4m3 rounding of C does not meet it.
+//   in the same TMEM accumulator.  Three terms carry ~12 significant bits of every element
+//   and leave a relative error of ~2e-5 on the GEMM2 result, below the ~1e-5 fp32
+//   summation-order noise of the definition itself by less than a factor of two and two
+//   orders of magnitude inside the output tolerance; a single e4m3 rounding of C (what a
+//   plain fp8 x fp8 GEMM2 would use) does not meet it.  The reference kernel keeps C in a
+//   bf16 hi+lo pair for the same reason (moe.cu:1241-1251).  Each extra plane costs a
+//   quarter more L2->SM traffic for GEMM2's token operand, which bounds it at large T.
 // combine: out[t] = bf16( sum over the token's local experts, ascending, of
 //   weight * (sum of GEMM2 split-K slabs) ), the accumulation order of
 //   references/moe.py:168-200; replaces the fp32 atomics of the reference GEMM2
