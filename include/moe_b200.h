@@ -74,6 +74,14 @@ int moe_fp8_block_scale_route(const float* routing_logits, const uint16_t* routi
                               int local_expert_offset, float routed_scaling_factor,
                               int32_t* topk_idx, float* topk_w, uint32_t* local_mask, void* stream);
 
+/* The step before the operator: bf16 activations [T, 7168] -> e4m3 [T, 7168] plus one
+ * fp32 scale per (token, 128-column block) in the definition's transposed layout
+ * [56, T] (full-agent-pipeline/references/moe.py:32-33, 95-104): scale = amax / 448,
+ * q = e4m3(x / scale).  The reference has no kernel for this step (its harness
+ * generates the layout on the host).  Asynchronous on `stream`. */
+int moe_fp8_block_scale_quantize_activations(const uint16_t* hidden_bf16, int T, uint8_t* hidden_states,
+                                             float* hidden_states_scale, void* stream);
+
 /* Waits for `stream` and returns the error bits the kernels of the last call on
  * this workspace recorded (0 = none) in *status.  The reference checks no CUDA
  * return code at all (moe.cu:2729-2894); this is the replacement's error channel. */

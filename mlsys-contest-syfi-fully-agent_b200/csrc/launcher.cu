@@ -51,6 +51,8 @@ void stage_mark(int i, cudaStream_t stream) {
     }                                                    \
   } while (0)
 
+constexpr size_t kPackLimit = 256 * 1024;   // ..._run_host packs its inputs into one copy up to this size
+
 // Staging area for ..._run_host, appended to the kernel workspace.
 struct HostStage {
   size_t logits, bias, hidden, hscale, out, total;
@@ -386,10 +388,24 @@ extern "C" int moe_fp8_block_scale_run_host(const float* routing_logits_host, co
   float* d_hscale = reinterpret_cast<float*>(ws + st.hscale);
   uint16_t* d_out = reinterpret_cast<uint16_t*>(ws + st.out);
   const size_t Tz = static_cast<size_t>(T);
-  MOE_CUDA(cudaMemcpyAsync(d_logits, routing_logits_host, Tz * kEGlobal * 4, cudaMemcpyHostToDevice, stream));
-  MOE_CUDA(cudaMemcpyAsync(d_bias, routing_bias_host, kEGlobal * 2, cudaMemcpyHostToDevice, stream));
-  MOE_CUDA(cudaMemcpyAsync(d_hidden, hidden_states_host, Tz * kH, cudaMemcpyHostToDevice, stream));
-  MOE_CUDA(cudaMemcpyAsync(d_hscale, hidden_states_scale_host, Tz * kKB1 * 4, cudaMemcpyHostToDevice, stream));
+  const size_t in_bytes = st.out - st.logits;     // logits | bias | hidden | scales are contiguous in the staging area
+  if (in_bytes <= kPackLimit) {
+    // Small batches: one copy instead of four.  The inputs are packed into a pinned block owned by
+    // this thread (allocated once) at the offsets of the device staging area.
+    static thread_local uint8_t* pinned = nullptr;
+    if (pinned == nullptr) MOE_CUDA(cudaHostAlloc(reinterpret_cast<void**>(&pinned), kPackLimit, cudaHostAllocDefault));
+    MOE_CUDA(cudaStreamSynchronize(stream));        // the previous call's copy may still read the block
+    std::memcpy(pinned, routing_logits_host, Tz * kEGlobal * 4);
+    std::memcpy(pinned + (st.bias - st.logits), routing_bias_host, kEGlobal * 2);
+    std::memcpy(pinned + (st.hidden - st.logits), hidden_states_host, Tz * kH);
+    std::memcpy(pinned + (st.hscale - st.logits), hidden_states_scale_host, Tz * kKB1 * 4);
+    MOE_CUDA(cudaMemcpyAsync(ws + st.logits, pinned, in_bytes, cudaMemcpyHostToDevice, stream));
+  } else {
+    MOE_CUDA(cudaMemcpyAsync(d_logits, routing_logits_host, Tz * kEGlobal * 4, cudaMemcpyHostToDevice, stream));
+    MOE_CUDA(cudaMemcpyAsync(d_bias, routing_bias_host, kEGlobal * 2, cudaMemcpyHostToDevice, stream));
+    MOE_CUDA(cudaMemcpyAsync(d_hidden, hidden_states_host, Tz * kH, cudaMemcpyHostToDevice, stream));
+    MOE_CUDA(cudaMemcpyAsync(d_hscale, hidden_states_scale_host, Tz * kKB1 * 4, cudaMemcpyHostToDevice, stream));
+  }
   int rc = moe_fp8_block_scale_run(d_logits, d_bias, d_hidden, d_hscale, gemm1_weights, gemm1_weights_scale,
                                    gemm2_weights, gemm2_weights_scale, T, local_expert_offset, routed_scaling_factor,
                                    d_out, workspace, workspace_bytes, stream_v);

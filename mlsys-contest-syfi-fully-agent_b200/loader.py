@@ -28,6 +28,7 @@ EXPORTS = [
     "moe_fp8_block_scale_stage_times",
     "moe_fp8_block_scale_route_static",
     "moe_fp8_block_scale_route",
+    "moe_fp8_block_scale_quantize_activations",
 ]
 STATIC_MAX_TOKENS = 4096
 STAGES = ("route_permute", "gather", "gemm1", "swiglu_split", "gemm2", "combine")
@@ -80,6 +81,8 @@ def _load() -> ctypes.CDLL:
     lib.moe_fp8_block_scale_route_static.argtypes = [vp, vp, i32, i32, f32, vp, vp, vp, vp, vp, vp]
     lib.moe_fp8_block_scale_route.restype = i32
     lib.moe_fp8_block_scale_route.argtypes = [vp, vp, i32, i32, f32, vp, vp, vp, vp]
+    lib.moe_fp8_block_scale_quantize_activations.restype = i32
+    lib.moe_fp8_block_scale_quantize_activations.argtypes = [vp, i32, vp, vp, vp]
     lib.moe_fp8_block_scale_launch_count.restype = ctypes.c_longlong
     lib.moe_fp8_block_scale_launch_count.argtypes = []
     lib.moe_fp8_block_scale_set_profiling.restype = i32

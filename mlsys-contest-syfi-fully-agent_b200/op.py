@@ -160,6 +160,21 @@ def route(routing_logits: torch.Tensor, routing_bias: torch.Tensor, local_expert
     return idx, w, mask
 
 
+def quantize_activations(hidden_bf16: torch.Tensor):
+    """bf16 [T, 7168] -> (e4m3 [T, 7168], fp32 scales [56, T]) in the operator's input layout."""
+    _check(hidden_bf16.dtype == torch.bfloat16 and hidden_bf16.dim() == 2 and hidden_bf16.shape[1] == H and
+           hidden_bf16.is_contiguous() and hidden_bf16.is_cuda, "hidden must be a contiguous CUDA bfloat16 [T, 7168]")
+    T = hidden_bf16.shape[0]
+    dev = hidden_bf16.device
+    q = torch.empty((T, H), dtype=torch.float8_e4m3fn, device=dev)
+    s = torch.empty((H // BLOCK, T), dtype=torch.float32, device=dev)
+    if T:
+        with torch.cuda.device(dev):
+            loader.check(loader.lib.moe_fp8_block_scale_quantize_activations(
+                hidden_bf16.data_ptr(), int(T), q.data_ptr(), s.data_ptr(), torch.cuda.current_stream(dev).cuda_stream))
+    return q, s
+
+
 def kernel_status(workspace: Optional[Workspace] = None, device=None) -> int:
     """Waits for the current stream and returns the kernels' error bits (0 = none)."""
     dev = torch.device(device if device is not None else "cuda")

@@ -232,3 +232,17 @@ def test_tvm_ffi_entry_point_matches_c_abi(pkg, dev, W):
                 W.gemm1_weights, W.gemm1_weights_scale, W.gemm2_weights, W.gemm2_weights_scale, 32, RSF, out)
         torch.cuda.synchronize()
         assert torch.equal(out.view(torch.int16), want.view(torch.int16))
+
+
+@pytest.mark.parametrize("T", [1, 7, 130, 4096])
+def test_activation_quantisation_is_bit_exact(pkg, dev, T):
+    """The quantisation kernel (the step before the operator) reproduces the generator's
+    reference quantisation bit for bit: e4m3 bytes and the transposed [56, T] scales."""
+    x = (pkg.gen.normal(21, 9, 0, T * 7168, dev).view(T, 7168) * 3.0).to(torch.bfloat16)
+    x[0, :128] = 0                     # an all-zero block: scale floor, zeros out
+    if T > 1:
+        x[1, 5] = 30000.0              # a large outlier in a block
+    q, s = pkg.op.quantize_activations(x.contiguous())
+    q_ref, s_ref = pkg.gen.quant_1x128(x.to(torch.float32))
+    assert torch.equal(s, s_ref.t().contiguous())
+    assert torch.equal(q.view(torch.uint8), q_ref.view(torch.uint8))
