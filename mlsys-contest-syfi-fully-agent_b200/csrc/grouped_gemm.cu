@@ -114,7 +114,11 @@ static_assert(sizeof(Aux) <= 1024, "Aux must fit its slot");
 
 // Extra shared state of the decode-fused kernels: every CTA routes all (<= 16) tokens itself.
 struct FusedAux {
-  float bias[kEGlobal];
+  uint32_t keys[kEGlobal];            // order-preserving keys of the biased scores of the token being routed
+  float sval[kEGlobal];               // its unbiased sigmoid scores
+  float gscore[kNGroup];
+  int selidx[kTopK];
+  float sels[kTopK];
   int tidx[kFusedMaxTokens][kTopK];
   float tw[kFusedMaxTokens][kTopK];
   uint32_t mask[kFusedMaxTokens];     // per token: selected local experts
@@ -235,25 +239,106 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
     // Decode path: no routing / permutation / gather kernels ran.  Every CTA routes all tokens and
     // derives the same schedule in shared memory; CTA 0 also publishes it for the later kernel.
     static_assert(N_TILE == kFusedMaxTokens, "the fused path puts every token in one token tile");
-    for (int i = threadIdx.x; i < kEGlobal; i += kThreads)
-      fa->bias[i] = __uint_as_float(static_cast<uint32_t>(a.bias_bf16[i]) << 16);
-    __syncthreads();
-    if (threadIdx.x == 0) TRACE(3, 6);
-    for (int t = warp; t < a.T; t += kThreads / 32) {
-      int idx;
-      float w;
-      route_token(a.logits + static_cast<size_t>(t) * kEGlobal, fa->bias, a.routed_scaling_factor, lane, idx, w);
-      uint32_t bit = 0;
-      if (lane < kTopK) {
-        fa->tidx[t][lane] = idx;
-        fa->tw[t][lane] = w;
-        const int le = idx - a.local_expert_offset;
-        if (le >= 0 && le < kELocal) bit = 1u << le;
+    if (a.T <= 2) {
+      // Block-cooperative routing (same arithmetic and tie rules as route_token): thread e < 256 owns
+      // expert e, so warp g is routing group g.  Per token: sigmoid + bias, the group's two best by
+      // two warp reductions, then every kept expert counts how many kept experts beat it; the eight
+      // with rank < 8 are the selection in descending order.  ~1k cycles per token instead of the
+      // ~7k of one warp doing eight rounds of arg-max.
+      const int e = threadIdx.x;
+      float* xs = reinterpret_cast<float*>(smem);                 // [T][256] logits; the stage ring is still idle
+      float bias_e = 0.0f;
+      if (e < kEGlobal) {
+        bias_e = __uint_as_float(static_cast<uint32_t>(a.bias_bf16[e]) << 16);
+        for (int t = 0; t < a.T; ++t) xs[t * kEGlobal + e] = a.logits[static_cast<size_t>(t) * kEGlobal + e];
       }
-      bit = __reduce_or_sync(0xFFFFFFFFu, bit);
-      if (lane == 0) fa->mask[t] = bit;
+      if (threadIdx.x == 0) TRACE(3, 6);
+      for (int t = 0; t < a.T; ++t) {
+        float s_e = 0.0f;
+        uint32_t key_e = 0;
+        if (e < kEGlobal) {
+          s_e = 1.0f / (1.0f + expf(-xs[t * kEGlobal + e]));
+          key_e = order_key(s_e + bias_e);
+          fa->keys[e] = key_e;
+          fa->sval[e] = s_e;
+          const uint32_t k1 = __reduce_max_sync(0xFFFFFFFFu, key_e);
+          const int first = __ffs(__ballot_sync(0xFFFFFFFFu, key_e == k1)) - 1;
+          const uint32_t k2 = __reduce_max_sync(0xFFFFFFFFu, lane == first ? 0u : key_e);
+          const uint32_t u1 = (k1 & 0x80000000u) ? (k1 & 0x7FFFFFFFu) : ~k1;
+          const uint32_t u2 = (k2 & 0x80000000u) ? (k2 & 0x7FFFFFFFu) : ~k2;
+          if (lane == 0) fa->gscore[warp] = __uint_as_float(u1) + __uint_as_float(u2);
+        }
+        __syncthreads();
+        if (e < kEGlobal) {
+          uint32_t keep = 0;
+  #pragma unroll
+          for (int g = 0; g < kNGroup; ++g) {
+            int rank = 0;
+  #pragma unroll
+            for (int h2 = 0; h2 < kNGroup; ++h2)
+              rank += (fa->gscore[h2] > fa->gscore[g]) || (fa->gscore[h2] == fa->gscore[g] && h2 < g);
+            keep |= (rank < kTopKGroup ? 1u : 0u) << g;
+          }
+          if ((keep >> warp) & 1u) {
+            int rank = 0;
+            for (int g = 0; g < kNGroup; ++g) {
+              if (!((keep >> g) & 1u)) continue;
+              const uint4* kv = reinterpret_cast<const uint4*>(fa->keys + g * 32);
+  #pragma unroll
+              for (int c = 0; c < 8; ++c) {
+                const uint4 k = kv[c];
+                const int j = g * 32 + c * 4;
+                rank += (k.x > key_e) || (k.x == key_e && j + 0 < e);
+                rank += (k.y > key_e) || (k.y == key_e && j + 1 < e);
+                rank += (k.z > key_e) || (k.z == key_e && j + 2 < e);
+                rank += (k.w > key_e) || (k.w == key_e && j + 3 < e);
+              }
+            }
+            if (rank < kTopK) { fa->selidx[rank] = e; fa->sels[rank] = s_e; }
+          }
+        }
+        __syncthreads();
+        if (warp == 0) {
+          const float sv = lane < kTopK ? fa->sels[lane] : 0.0f;
+          float sum = 0.0f;
+  #pragma unroll
+          for (int k = 0; k < kTopK; ++k) sum += __shfl_sync(0xFFFFFFFFu, sv, k);
+          sum += 1e-20f;
+          uint32_t bit = 0;
+          if (lane < kTopK) {
+            const int idx = fa->selidx[lane];
+            fa->tidx[t][lane] = idx;
+            fa->tw[t][lane] = (sv / sum) * a.routed_scaling_factor;
+            const int le = idx - a.local_expert_offset;
+            if (le >= 0 && le < kELocal) bit = 1u << le;
+          }
+          bit = __reduce_or_sync(0xFFFFFFFFu, bit);
+          if (lane == 0) fa->mask[t] = bit;
+        }
+      }
+    } else {
+      // More than two tokens: one warp per token (ten at a time), each doing the warp-level routing.
+      float* bias_s = fa->sval;                                  // 256 floats, free on this path
+      for (int i = threadIdx.x; i < kEGlobal; i += kThreads)
+        bias_s[i] = __uint_as_float(static_cast<uint32_t>(a.bias_bf16[i]) << 16);
+      __syncthreads();
+      for (int t = warp; t < a.T; t += kThreads / 32) {
+        int idx;
+        float w;
+        route_token(a.logits + static_cast<size_t>(t) * kEGlobal, bias_s, a.routed_scaling_factor, lane, idx, w);
+        uint32_t bit = 0;
+        if (lane < kTopK) {
+          fa->tidx[t][lane] = idx;
+          fa->tw[t][lane] = w;
+          const int le = idx - a.local_expert_offset;
+          if (le >= 0 && le < kELocal) bit = 1u << le;
+        }
+        bit = __reduce_or_sync(0xFFFFFFFFu, bit);
+        if (lane == 0) fa->mask[t] = bit;
+      }
     }
     if (threadIdx.x == 0) TRACE(3, 7);
+    fence_proxy_async_smem();   // the logits scratch is about to be overwritten by TMA (async proxy)
     __syncthreads();
     if (threadIdx.x == 0) TRACE(3, 8);
     if (warp == 0) {                     // lane = local expert
