@@ -76,6 +76,7 @@ struct Cfg {
   static constexpr int KPS = (2 * KB_BYTES <= 64 * 1024 && 2 * KB_COLS <= 256) ? 2 : 1;
   static constexpr int G = KPS;
   static constexpr int CPW = N_TILE / 2;                                // token columns per epilogue warp
+  static constexpr int CH = CPW > 64 ? 32 : CPW;                        // columns read back per tcgen05.ld batch
   static constexpr int STAGE_BYTES = KPS * KB_BYTES;
   static constexpr int SC_BUFS = N_TILE <= 32 ? 2 : 1;                  // scale-product tables
   static constexpr int SC_BYTES = SC_BUFS * KB * N_TILE * 4;
@@ -374,9 +375,12 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
         sched->counts[lane] = c;
         sched->offs[lane + 1] = inc;
         sched->tile_prefix[lane + 1] = tinc;
+        sched->tile_prefix2[lane + 1] = tinc;
         if (lane == 0) {
           sched->offs[0] = 0;
           sched->tile_prefix[0] = 0;
+          sched->tile_prefix2[0] = 0;
+          sched->n_tile2 = N_TILE;
           sched->status = 0;
           sched->n_sel = n_sel;
           sched->n_sel_pad = pad;
@@ -421,7 +425,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
     split = GEMM == 1 ? sched->split1 : sched->split2;
     n_sel_pad = sched->n_sel_pad;
     if (threadIdx.x <= kELocal) {
-      aux->prefix[threadIdx.x] = sched->tile_prefix[threadIdx.x];
+      aux->prefix[threadIdx.x] = GEMM == 1 ? sched->tile_prefix[threadIdx.x] : sched->tile_prefix2[threadIdx.x];
       aux->offs[threadIdx.x] = sched->offs[threadIdx.x];
     }
   }
@@ -569,32 +573,36 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
         const uint32_t taddr = tmem_base + lane_addr + buf * (C::G * C::KB_COLS) + h * C::CPW;
 #pragma unroll
         for (int g = 0; g < C::G; ++g) {
-          // one K-block's partial at a time (register budget); the buffer is released after the last read
-          float v[C::PLANES][C::CPW];
+          // one K-block's partial at a time, in chunks of at most 64 columns (register budget);
+          // the buffer is released after the last read
 #pragma unroll
-          for (int p = 0; p < C::PLANES; ++p) tmem_ld_cols<C::CPW>(taddr + g * C::KB_COLS + p * N_TILE, v[p]);
-          tmem_wait_ld();
-          if (g == C::G - 1) {
-            tc_fence_before_sync();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(tempty_base + buf * 8);
-          }
-          const float4* scv = reinterpret_cast<const float4*>(sc + (kbl + g) * N_TILE + h * C::CPW);
+          for (int c0 = 0; c0 < C::CPW; c0 += C::CH) {
+            float v[C::PLANES][C::CH];
 #pragma unroll
-          for (int u = 0; u < C::CPW / 4; ++u) {
-            const float4 f = scv[u];
-            float s4[4];
-#pragma unroll
-            for (int x = 0; x < 4; ++x) {
-              float sum = v[C::PLANES - 1][u * 4 + x];
-#pragma unroll
-              for (int p = C::PLANES - 2; p >= 0; --p) sum += v[p][u * 4 + x];   // smallest terms first
-              s4[x] = sum;
+            for (int p = 0; p < C::PLANES; ++p) tmem_ld_cols<C::CH>(taddr + g * C::KB_COLS + p * N_TILE + c0, v[p]);
+            tmem_wait_ld();
+            if (g == C::G - 1 && c0 + C::CH >= C::CPW) {
+              tc_fence_before_sync();
+              __syncwarp();
+              if (lane == 0) mbar_arrive(tempty_base + buf * 8);
             }
-            acc[u * 4 + 0] = fmaf(s4[0], f.x, acc[u * 4 + 0]);
-            acc[u * 4 + 1] = fmaf(s4[1], f.y, acc[u * 4 + 1]);
-            acc[u * 4 + 2] = fmaf(s4[2], f.z, acc[u * 4 + 2]);
-            acc[u * 4 + 3] = fmaf(s4[3], f.w, acc[u * 4 + 3]);
+            const float4* scv = reinterpret_cast<const float4*>(sc + (kbl + g) * N_TILE + h * C::CPW + c0);
+#pragma unroll
+            for (int u = 0; u < C::CH / 4; ++u) {
+              const float4 f = scv[u];
+              float s4[4];
+#pragma unroll
+              for (int x = 0; x < 4; ++x) {
+                float sum = v[C::PLANES - 1][u * 4 + x];
+#pragma unroll
+                for (int p = C::PLANES - 2; p >= 0; --p) sum += v[p][u * 4 + x];   // smallest terms first
+                s4[x] = sum;
+              }
+              acc[c0 + u * 4 + 0] = fmaf(s4[0], f.x, acc[c0 + u * 4 + 0]);
+              acc[c0 + u * 4 + 1] = fmaf(s4[1], f.y, acc[c0 + u * 4 + 1]);
+              acc[c0 + u * 4 + 2] = fmaf(s4[2], f.z, acc[c0 + u * 4 + 2]);
+              acc[c0 + u * 4 + 3] = fmaf(s4[3], f.w, acc[c0 + u * 4 + 3]);
+            }
           }
         }
         if (++stage == C::STAGES) { stage = 0; ph ^= 1u; }
@@ -707,7 +715,7 @@ extern "C" int moe_debug_trace(unsigned long long* host, int bytes) {
 int grouped_gemm_kblocks_per_stage(int gemm_id, int n_tile) {
 #define MOE_CASE(G, N) \
   if (gemm_id == G && n_tile == N) return Cfg<G, N>::KPS;
-  MOE_CASE(1, 16) MOE_CASE(1, 32) MOE_CASE(1, 64) MOE_CASE(1, 128)
+  MOE_CASE(1, 16) MOE_CASE(1, 32) MOE_CASE(1, 64) MOE_CASE(1, 128) MOE_CASE(1, 256)
   MOE_CASE(2, 16) MOE_CASE(2, 32) MOE_CASE(2, 64) MOE_CASE(2, 128)
 #undef MOE_CASE
   return 1;
@@ -719,6 +727,7 @@ int grouped_gemm_init() {
   if ((rc = init_one<1, 32>())) return rc;
   if ((rc = init_one<1, 64>())) return rc;
   if ((rc = init_one<1, 128>())) return rc;
+  if ((rc = init_one<1, 256>())) return rc;
   if ((rc = init_one<2, 16>())) return rc;
   if ((rc = init_one<2, 32>())) return rc;
   if ((rc = init_one<2, 64>())) return rc;
@@ -737,7 +746,7 @@ int launch_grouped_gemm(int gemm_id, int n_tile, const CUtensorMap& tm_w, const 
                         int ctas, cudaStream_t stream) {
 #define MOE_CASE(G, N) \
   if (gemm_id == G && n_tile == N) return launch_one<G, N>(tm_w, tm_b, a, ctas, stream);
-  MOE_CASE(1, 16) MOE_CASE(1, 32) MOE_CASE(1, 64) MOE_CASE(1, 128)
+  MOE_CASE(1, 16) MOE_CASE(1, 32) MOE_CASE(1, 64) MOE_CASE(1, 128) MOE_CASE(1, 256)
   MOE_CASE(2, 16) MOE_CASE(2, 32) MOE_CASE(2, 64) MOE_CASE(2, 128)
 #undef MOE_CASE
   return static_cast<int>(cudaErrorInvalidValue);

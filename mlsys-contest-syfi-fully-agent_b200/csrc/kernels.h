@@ -50,7 +50,7 @@ struct RouteArgs {
 struct PermuteArgs {
   int T;
   int local_expert_offset;
-  int n_tile;                   // token-tile width the GEMMs will use
+  int n_tile, n_tile2;          // token-tile widths GEMM1 / GEMM2 will use
   int ctas;                     // persistent CTAs the GEMMs will run
   int kps1, kps2;               // K-blocks per pipeline stage of the two GEMM kernels (split granularity)
   int rows_cap, slab_rows;
@@ -116,7 +116,7 @@ struct CombineArgs {
 void launch_route_permute(const RouteArgs& r, const PermuteArgs& p, cudaStream_t stream);
 void launch_route_only(const RouteArgs& r, cudaStream_t stream);
 void launch_gather_rows(const GatherArgs& a, int T, cudaStream_t stream);
-// gemm_id 1 or 2; n_tile in {16, 32, 64, 128}.  Returns a cudaError_t as int.
+// gemm_id 1 or 2; n_tile in {16, 32, 64, 128} (GEMM1 also 256).  Returns a cudaError_t as int.
 int launch_grouped_gemm(int gemm_id, int n_tile, const CUtensorMap& tm_w, const CUtensorMap& tm_b, const GemmArgs& a,
                         int ctas, cudaStream_t stream);
 // Decode path (T <= 16): GEMM1 with in-kernel routing and a SwiGLU tail, GEMM2 with a combine tail.

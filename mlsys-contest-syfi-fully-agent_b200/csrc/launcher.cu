@@ -191,7 +191,9 @@ int pick_n_tile(int T) {
     const char* s = std::getenv("MOE_B200_NTILE");
     return s ? std::atoi(s) : 0;
   }();
-  if (forced == 16 || forced == 32 || forced == 64 || forced == 128) return forced;
+  if (forced == 16 || forced == 32 || forced == 64 || forced == 128 || forced == 256) return forced;
+  // 256-token tiles (GEMM1 only) exist for experiments (MOE_B200_NTILE=256); with eight promotion warps
+  // they are slower than 128-token tiles (the read-back of 256 TMEM columns per K-block dominates)
   return T <= 16 ? 16 : T <= 32 ? 32 : T <= 64 ? 64 : 128;
 }
 
@@ -280,16 +282,17 @@ extern "C" int moe_fp8_block_scale_run(const float* routing_logits, const uint16
   float* o = reinterpret_cast<float*>(ws + L.o);
 
   const int n_tile = pick_n_tile(T);
+  const int n_tile2 = n_tile > 128 ? 128 : n_tile;   // GEMM2's three-plane token operand does not fit 256-token stages
   const int ctas = dev->sm_count;
 
   CUtensorMap tm_w13, tm_w2, tm_a, tm_c;
-  const uint32_t kps1 = grouped_gemm_kblocks_per_stage(1, n_tile), kps2 = grouped_gemm_kblocks_per_stage(2, n_tile);
+  const uint32_t kps1 = grouped_gemm_kblocks_per_stage(1, n_tile), kps2 = grouped_gemm_kblocks_per_stage(2, n_tile2);
   if ((rc = get_map(dev, kblock_map(gemm1_weights, static_cast<uint64_t>(kELocal) * k2I, kH, 128, kps1), &tm_w13)))
     return rc;
   if ((rc = get_map(dev, kblock_map(gemm2_weights, static_cast<uint64_t>(kELocal) * kH, kI, 128, kps2), &tm_w2)))
     return rc;
   if ((rc = get_map(dev, kblock_map(a_packed, L.rows_cap, kH, n_tile, kps1), &tm_a))) return rc;
-  if ((rc = get_map(dev, planes_map(cq, L.rows_cap, n_tile, kps2), &tm_c))) return rc;
+  if ((rc = get_map(dev, planes_map(cq, L.rows_cap, n_tile2, kps2), &tm_c))) return rc;
 
   if (T <= kFusedMaxTokens && use_fused_decode()) {
     // Decode path: two launches.  GEMM1 routes in-kernel, reads the token rows straight from
@@ -320,7 +323,7 @@ extern "C" int moe_fp8_block_scale_run(const float* routing_logits, const uint16
 
   RouteArgs ra{routing_logits, routing_bias, T, local_expert_offset, routed_scaling_factor, topk_idx, topk_w,
                local_mask};
-  PermuteArgs pa{T, local_expert_offset, n_tile, ctas, static_cast<int>(kps1), static_cast<int>(kps2), L.rows_cap, L.slab_rows, local_mask, topk_idx, topk_w,
+  PermuteArgs pa{T, local_expert_offset, n_tile, n_tile2, ctas, static_cast<int>(kps1), static_cast<int>(kps2), L.rows_cap, L.slab_rows, local_mask, topk_idx, topk_w,
                  sched, perm_token, perm_weight, tok_rows};
   stage_mark(0, stream);
   launch_route_permute(ra, pa, stream);
@@ -351,7 +354,7 @@ extern "C" int moe_fp8_block_scale_run(const float* routing_logits, const uint16
 
   GemmArgs g2a{};
   g2a.sched = sched; g2a.w_scale = gemm2_weights_scale; g2a.b_scale = c_scale; g2a.out = o;
-  if ((rc = launch_grouped_gemm(2, n_tile, tm_w2, tm_c, g2a, ctas, stream))) {
+  if ((rc = launch_grouped_gemm(2, n_tile2, tm_w2, tm_c, g2a, ctas, stream))) {
     g_last_cuda_error = rc;
     return MOE_B200_ECUDA;
   }

@@ -49,10 +49,12 @@ struct MoeSched {
   int items1, items2;      // work items of GEMM1 / GEMM2
   unsigned int bar1[2];    // grid barrier of the fused GEMM1 kernel: {arrivals, call tag}
   unsigned int bar2[2];    // same for the fused GEMM2 kernel
-  int pad_[2];
+  int n_tile2;             // token-tile width of GEMM2 (<= n_tile)
+  int pad_[1];
   int counts[kELocal];
   int offs[kELocal + 1];       // exclusive prefix of counts
-  int tile_prefix[kELocal + 1];  // exclusive prefix of token tiles
+  int tile_prefix[kELocal + 1];  // exclusive prefix of GEMM1 token tiles (width n_tile)
+  int tile_prefix2[kELocal + 1]; // exclusive prefix of GEMM2 token tiles (width n_tile2)
 };
 
 // Byte offsets of the workspace arrays for a given token count.

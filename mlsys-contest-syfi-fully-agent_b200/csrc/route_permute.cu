@@ -73,13 +73,14 @@ __device__ void permute_block(const PermuteArgs& a) {
     // lane = expert: totals over warps, exclusive scan over experts, per-warp first rows
     int c = 0;
     for (int w = 0; w < 32; ++w) c += s_wcount[w][lane];
-    const int tiles = (c + a.n_tile - 1) / a.n_tile;
-    int inc = c, tinc = tiles;
+    const int tiles = (c + a.n_tile - 1) / a.n_tile, tiles2 = (c + a.n_tile2 - 1) / a.n_tile2;
+    int inc = c, tinc = tiles, tinc2 = tiles2;
 #pragma unroll
     for (int d = 1; d < 32; d <<= 1) {
       const int v = __shfl_up_sync(0xFFFFFFFFu, inc, d);
       const int tv = __shfl_up_sync(0xFFFFFFFFu, tinc, d);
-      if (lane >= d) { inc += v; tinc += tv; }
+      const int tv2 = __shfl_up_sync(0xFFFFFFFFu, tinc2, d);
+      if (lane >= d) { inc += v; tinc += tv; tinc2 += tv2; }
     }
     int run = inc - c;                          // first row of expert `lane`
     for (int w = 0; w < 32; ++w) {
@@ -91,14 +92,18 @@ __device__ void permute_block(const PermuteArgs& a) {
     sc->counts[lane] = c;
     sc->offs[lane + 1] = inc;
     sc->tile_prefix[lane + 1] = tinc;
+    sc->tile_prefix2[lane + 1] = tinc2;
     const uint32_t act = __ballot_sync(0xFFFFFFFFu, c > 0);
     const int n_sel = __shfl_sync(0xFFFFFFFFu, inc, 31), tiles_total = __shfl_sync(0xFFFFFFFFu, tinc, 31);
+    const int tiles_total2 = __shfl_sync(0xFFFFFFFFu, tinc2, 31);
     const int n_sel_pad = (n_sel + 15) & ~15;
     const int s1 = choose_split_warp(tiles_total * kMT1, kMaxSplit1, a.ctas, n_sel_pad, a.slab_rows, lane, kKB1, a.kps1);
-    const int s2 = choose_split_warp(tiles_total * kMT2, kMaxSplit2, a.ctas, n_sel_pad, a.slab_rows, lane, kKB2, a.kps2);
+    const int s2 = choose_split_warp(tiles_total2 * kMT2, kMaxSplit2, a.ctas, n_sel_pad, a.slab_rows, lane, kKB2, a.kps2);
     if (lane == 31) {
       sc->offs[0] = 0;
       sc->tile_prefix[0] = 0;
+      sc->tile_prefix2[0] = 0;
+      sc->n_tile2 = a.n_tile2;
       sc->status = (n_sel > a.rows_cap) ? kErrSchedOverflow : 0;
       sc->n_sel = n_sel;
       sc->n_sel_pad = n_sel_pad;
@@ -108,7 +113,7 @@ __device__ void permute_block(const PermuteArgs& a) {
       sc->split1 = s1;
       sc->split2 = s2;
       sc->items1 = tiles_total * kMT1 * s1;
-      sc->items2 = tiles_total * kMT2 * s2;
+      sc->items2 = tiles_total2 * kMT2 * s2;
     }
   }
   __syncthreads();

@@ -82,7 +82,7 @@ extern "C" int moe_fp8_block_scale_route_static(const float* routing_logits, con
   const int rows_cap = T * kTopK;
   RouteArgs ra{routing_logits, routing_bias, T, local_expert_offset, routed_scaling_factor, topk_idx, topk_w,
                local_mask};
-  PermuteArgs pa{T, local_expert_offset, 128, kNumSMs, 1, 1, rows_cap, rows_cap > kMinSlabRows ? rows_cap : kMinSlabRows,
+  PermuteArgs pa{T, local_expert_offset, 128, 128, kNumSMs, 1, 1, rows_cap, rows_cap > kMinSlabRows ? rows_cap : kMinSlabRows,
                  local_mask, topk_idx, topk_w, sched, perm_token, perm_weight, tok_rows};
   launch_route_permute(ra, pa, stream);
   if (cudaGetLastError() != cudaSuccess) return MOE_B200_ECUDA;

@@ -43,7 +43,7 @@ def test_workspace_size_and_layout(loader):
                 L.a_packed, L.a_scale_rows, L.g1, L.cq, L.c_scale, L.o]
         assert offs == sorted(offs) and all(o % 1024 == 0 for o in offs) and offs[-1] < n
     assert loader.workspace_bytes(-1) == 0
-    assert ctypes.sizeof(loader.Sched) == (16 + 32 + 33 + 33) * 4
+    assert ctypes.sizeof(loader.Sched) == (16 + 32 + 33 + 33 + 33) * 4
 
 
 def test_bad_arguments_are_rejected_without_a_device(loader):
