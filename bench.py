@@ -280,6 +280,9 @@ def bench_single(args):
     }
     if args.sweep:
         line["sweep"] = sweep(pkg, W, [n for n in WORKLOADS if n != name], peak)
+        del W, reps
+        torch.cuda.empty_cache()
+        line["ep_layer_single_gpu"] = ep_single_gpu(pkg, dev)
     print(json.dumps(line))
 
 
@@ -319,6 +322,22 @@ def sweep(pkg, W, names, peak):
                      "stage_us": acc})
         del reps
     return rows
+
+
+def ep_single_gpu(pkg, dev, steps=3):
+    """The 256-expert layer of the multi-GPU workload (T = 16384) on ONE GPU: eight shard calls
+    per layer call, no communication.  The N = 1 point of the expert-parallel scaling curve."""
+    gen, ep = pkg.gen, pkg.ep
+    T = 16384
+    weights = [gen.make_shard_weights(1000 + s, dev) for s in range(8)]
+    tok = gen.make_tokens(T, 0, dev)
+    layer = ep.ExpertParallelMoE(weights, 0, 1)
+
+    def step(i=0):
+        return layer.forward(tok.routing_logits, tok.routing_bias, tok.hidden_states, tok.hidden_states_scale, RSF)
+    ms = time_steps(step, steps, 2)
+    return {"workload": "ep_layer_t16384", "n_gpus": 1, "ms_per_step": ms, "tokens_per_s": T / (ms * 1e-3),
+            "records": int(sum(layer.last_plan.recv_counts))}
 
 
 def bench_reference(args):

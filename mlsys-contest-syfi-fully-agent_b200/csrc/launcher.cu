@@ -409,11 +409,19 @@ extern "C" int moe_fp8_block_scale_run_host(const float* routing_logits_host, co
     MOE_CUDA(cudaMemcpyAsync(d_hidden, hidden_states_host, Tz * kH, cudaMemcpyHostToDevice, stream));
     MOE_CUDA(cudaMemcpyAsync(d_hscale, hidden_states_scale_host, Tz * kKB1 * 4, cudaMemcpyHostToDevice, stream));
   }
+  // Pinned (page-locked) host memory is addressable from the device, so the combine kernel can write
+  // the bf16 result straight into the caller's buffer and the device-to-host copy disappears; pageable
+  // buffers go through the staging area and one copy.
+  cudaPointerAttributes attr{};
+  const bool direct = Tz * kH * 2 <= kPackLimit && cudaPointerGetAttributes(&attr, output_host) == cudaSuccess &&
+                      attr.type == cudaMemoryTypeHost && attr.devicePointer != nullptr && aligned16(attr.devicePointer);
+  cudaGetLastError();   // a failed attribute query on pageable memory is not an error of this call
+  uint16_t* out_dev = direct ? static_cast<uint16_t*>(attr.devicePointer) : d_out;
   int rc = moe_fp8_block_scale_run(d_logits, d_bias, d_hidden, d_hscale, gemm1_weights, gemm1_weights_scale,
                                    gemm2_weights, gemm2_weights_scale, T, local_expert_offset, routed_scaling_factor,
-                                   d_out, workspace, workspace_bytes, stream_v);
+                                   out_dev, workspace, workspace_bytes, stream_v);
   if (rc != MOE_B200_OK) return rc;
-  MOE_CUDA(cudaMemcpyAsync(output_host, d_out, Tz * kH * 2, cudaMemcpyDeviceToHost, stream));
+  if (!direct) MOE_CUDA(cudaMemcpyAsync(output_host, d_out, Tz * kH * 2, cudaMemcpyDeviceToHost, stream));
   MOE_CUDA(cudaStreamSynchronize(stream));
   return MOE_B200_OK;
 }
