@@ -50,9 +50,9 @@ WORKLOADS = {
 
 # dram__bytes_read.sum + dram__bytes_write.sum of one GEMM1 launch, from the ncu capture
 # summarised in profiles/ (None until a capture of that workload exists).
-NCU_TRAFFIC_BYTES = {"decode_t1": 58_821_120 + 176_896,        # profiles/grouped_gemm_fused_decode_t1.md
-                     "skew_t64": 474_010_000 + 12_660_000,     # profiles/launch_shares_skew_t64_prefill_t4096.md
-                     "prefill_t4096": 808_470_000 + 67_240_000}
+NCU_TRAFFIC_BYTES = {"decode_t1": 58_828_288 + 54_528,        # profiles/grouped_gemm_fused_decode_t1.md
+                     "skew_t64": 473_900_000 + 12_600_000,     # profiles/launch_shares_skew_t64_prefill_t4096.md
+                     "prefill_t4096": 810_400_000 + 69_200_000}
 
 W13_BYTES = 4096 * 7168 + 32 * 56 * 4          # one expert's GEMM1 weights + scales
 W2_BYTES = 7168 * 2048 + 56 * 16 * 4
