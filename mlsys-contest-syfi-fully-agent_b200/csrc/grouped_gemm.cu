@@ -51,8 +51,19 @@ __device__ unsigned long long g_moe_trace[2][4][256];
 
 namespace {
 
+// Three warpgroups: warpgroup 0 holds the TMA producer (warp 0) and the UMMA issuer (warp 1) and gives
+// most of its registers away (setmaxnreg); warpgroups 1 and 2 are the eight promotion / epilogue warps
+// (warp % 4 = the TMEM lane quarter a warp may access) and take them.
 constexpr int kEpiWarps = 8;
-constexpr int kThreads = 64 + kEpiWarps * 32;   // producer warp + issuer warp + epilogue warps
+constexpr int kFirstEpiWarp = 4;
+constexpr int kThreads = (kFirstEpiWarp + kEpiWarps) * 32;
+constexpr int kRegsControl = 96;     // per thread in warpgroup 0 after the role split
+constexpr int kRegsEpilogue = 200;   // per thread in warpgroups 1 and 2
+// setmaxnreg.inc waits (unboundedly) for registers released by setmaxnreg.dec: the new total must fit
+// in what the launch allocated, 168 registers (the launch-bounds cap for 384 threads) per thread.
+constexpr int kRegsAtLaunch = 168;
+static_assert(128 * kRegsControl + 256 * kRegsEpilogue <= kRegsAtLaunch * kThreads, "register reallocation would never complete");
+static_assert(kRegsControl % 8 == 0 && kRegsEpilogue % 8 == 0, "setmaxnreg takes multiples of 8");
 
 template <int GEMM, int N_TILE>
 struct Cfg {
@@ -395,7 +406,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
       }
     }
     __syncthreads();
-    if (blockIdx.x == 0 && warp == 2 && lane < a.T) {   // lane = token: selection, permutation, row lists
+    if (blockIdx.x == 0 && warp == kFirstEpiWarp && lane < a.T) {   // lane = token: selection, permutation, row lists
       const int t = lane;
       const uint32_t m = fa->mask[t];
       a.local_mask[t] = m;
@@ -436,6 +447,8 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
   volatile int* abort_flag = &aux->abort;
   if (threadIdx.x == 0) TRACE(3, 1);
 
+  if (warp < kFirstEpiWarp) {
+  setmaxnreg_dec<kRegsControl>();
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
     if (lane == 0) {
@@ -501,11 +514,13 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
       }
     }
     __syncwarp();
+  }
   } else {
-    // ------------------------------------------------------------------ promotion + epilogue (warps 2..9)
+    setmaxnreg_inc<kRegsEpilogue>();
+    // ------------------------------------------------------------------ promotion + epilogue (warps 4..11)
     const int q = warp & 3;                       // TMEM lane quarter this warp may access
-    const int h = (warp - 2) >> 2;                // which half of the token columns
-    const int etid = threadIdx.x - 64;            // 0..255
+    const int h = (warp - kFirstEpiWarp) >> 2;    // which half of the token columns
+    const int etid = threadIdx.x - kFirstEpiWarp * 32;   // 0..255
     const uint32_t lane_addr = static_cast<uint32_t>(q * 32) << 16;
     uint32_t eph = 0, nitem = 0;
     uint32_t stage = 0, ph = 0, buf = 0, bph = 0;      // same ring positions as the issuer
@@ -647,7 +662,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
         if constexpr (GEMM == 1) {
           const int units = fa->n_sel * kKB2;
           const size_t slab = static_cast<size_t>(n_sel_pad) * k2I;
-          for (int u = blockIdx.x * kEpiWarps + (warp - 2); u < units; u += gridDim.x * kEpiWarps)
+          for (int u = blockIdx.x * kEpiWarps + (warp - kFirstEpiWarp); u < units; u += gridDim.x * kEpiWarps)
             swiglu_split_unit(a.out, slab, split, u / kKB2, u % kKB2, lane, a.cq, a.c_scale, a.rows_cap);
         } else {
           constexpr int kVec = kH / 4;
