@@ -139,7 +139,7 @@ int moe_fp8_block_scale_stage_times(float* ms, int n);
 /* No counterpart in the reference.  The routing / histogram / prefix-sum /
  * permutation stage for callers that cannot allocate device memory when they need
  * it (a plugin inside an engine that owns all memory, or code that runs while the
- * allocator is off limits): the stage's scratch lives in a fixed ~150 KB device
+ * allocator is off limits): the stage's scratch lives in a fixed ~160 KB device
  * array inside the library instead of a caller workspace.
  *   in : routing_logits f32 [T, 256], routing_bias bf16 [256]
  *   out: topk_idx i32 [T, 8], topk_w f32 [T, 8], expert_offsets i32 [33] (exclusive

@@ -15,53 +15,69 @@ __device__ __forceinline__ float from_e4m3(uint8_t b) {
   return __half2float(__half(h));
 }
 
-// SwiGLU + 4-term e4m3 split of one (row, 128-column block) by one warp; lane owns 4 columns.
-// `g1` points at the first split-K slab; slabs are `slab` floats apart.  Loads bypass L1
-// (the slabs may have been written by other SMs in the same kernel).
-__device__ __forceinline__ void swiglu_split_unit(const float* g1, size_t slab, int split, int row, int kb, int lane,
-                                                  uint8_t* cq, float* c_scale, int rows_cap) {
-  const float* p = g1 + static_cast<size_t>(row) * k2I + kb * kBlock + lane * 4;
-  float4 x1 = make_float4(0.f, 0.f, 0.f, 0.f), x2 = x1;
+// SwiGLU + e4m3 split of NB consecutive 128-column blocks of one row by one warp; lane owns 4
+// columns of each block.  `g1` points at the first split-K slab; slabs are `slab` floats apart.
+// All loads of the NB blocks are issued before any arithmetic (memory-level parallelism), and they
+// bypass L1 (the slabs may have been written by other SMs in the same kernel).
+template <int NB>
+__device__ __forceinline__ void swiglu_split_blocks(const float* g1, size_t slab, int split, int row, int kb0, int lane,
+                                                    uint8_t* cq, float* c_scale, int rows_cap) {
+  float4 x1[NB], x2[NB];
+#pragma unroll
+  for (int b = 0; b < NB; ++b) x1[b] = x2[b] = make_float4(0.f, 0.f, 0.f, 0.f);
   for (int s = 0; s < split; ++s) {
-    const float4 u = __ldcg(reinterpret_cast<const float4*>(p + s * slab));
-    const float4 v = __ldcg(reinterpret_cast<const float4*>(p + s * slab + kI));
-    x1.x += u.x; x1.y += u.y; x1.z += u.z; x1.w += u.w;
-    x2.x += v.x; x2.y += v.y; x2.z += v.z; x2.w += v.w;
-  }
-  float c[4];
-  c[0] = __fmul_rn(x2.x / (1.0f + expf(-x2.x)), x1.x);
-  c[1] = __fmul_rn(x2.y / (1.0f + expf(-x2.y)), x1.y);
-  c[2] = __fmul_rn(x2.z / (1.0f + expf(-x2.z)), x1.z);
-  c[3] = __fmul_rn(x2.w / (1.0f + expf(-x2.w)), x1.w);
-  float amax = fmaxf(fmaxf(fabsf(c[0]), fabsf(c[1])), fmaxf(fabsf(c[2]), fabsf(c[3])));
 #pragma unroll
-  for (int d = 16; d > 0; d >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, d));
-  // power-of-two scale with amax / scale in (224, 448]
-  int e = 0;
-  if (amax > 0.0f && amax < 3.0e38f) {
-    e = ilogbf(amax * (1.0f / 448.0f)) + 1;
-    e = max(-100, min(100, e));
-  }
-  const float scale = scalbnf(1.0f, e), inv = scalbnf(1.0f, -e);
-  uint32_t packed[kNTerms];
-#pragma unroll
-  for (int t = 0; t < kNTerms; ++t) packed[t] = 0;
-#pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    float r = c[i] * inv;
-    if (!(fabsf(r) <= 448.0f)) r = r > 0.0f ? 448.0f : (r < 0.0f ? -448.0f : 0.0f);   // inf / nan guard
-#pragma unroll
-    for (int t = 0; t < kNTerms; ++t) {
-      const uint8_t q = to_e4m3(r);
-      r -= from_e4m3(q);
-      packed[t] |= static_cast<uint32_t>(q) << (8 * i);
+    for (int b = 0; b < NB; ++b) {
+      const float* p = g1 + s * slab + static_cast<size_t>(row) * k2I + (kb0 + b) * kBlock + lane * 4;
+      const float4 u = __ldcg(reinterpret_cast<const float4*>(p));
+      const float4 v = __ldcg(reinterpret_cast<const float4*>(p + kI));
+      x1[b].x += u.x; x1[b].y += u.y; x1[b].z += u.z; x1[b].w += u.w;
+      x2[b].x += v.x; x2[b].y += v.y; x2[b].z += v.z; x2[b].w += v.w;
     }
   }
 #pragma unroll
-  for (int t = 0; t < kNTerms; ++t)
-    *reinterpret_cast<uint32_t*>(cq + (static_cast<size_t>(t) * rows_cap + row) * kI + kb * kBlock + lane * 4) =
-        packed[t];
-  if (lane == 0) c_scale[static_cast<size_t>(row) * kKB2 + kb] = scale;
+  for (int b = 0; b < NB; ++b) {
+    const int kb = kb0 + b;
+    float c[4];
+    c[0] = __fmul_rn(x2[b].x / (1.0f + expf(-x2[b].x)), x1[b].x);
+    c[1] = __fmul_rn(x2[b].y / (1.0f + expf(-x2[b].y)), x1[b].y);
+    c[2] = __fmul_rn(x2[b].z / (1.0f + expf(-x2[b].z)), x1[b].z);
+    c[3] = __fmul_rn(x2[b].w / (1.0f + expf(-x2[b].w)), x1[b].w);
+    float amax = fmaxf(fmaxf(fabsf(c[0]), fabsf(c[1])), fmaxf(fabsf(c[2]), fabsf(c[3])));
+#pragma unroll
+    for (int d = 16; d > 0; d >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, d));
+    // power-of-two scale with amax / scale in (224, 448]
+    int e = 0;
+    if (amax > 0.0f && amax < 3.0e38f) {
+      e = ilogbf(amax * (1.0f / 448.0f)) + 1;
+      e = max(-100, min(100, e));
+    }
+    const float scale = scalbnf(1.0f, e), inv = scalbnf(1.0f, -e);
+    uint32_t packed[kNTerms];
+#pragma unroll
+    for (int t = 0; t < kNTerms; ++t) packed[t] = 0;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      float r = c[i] * inv;
+      if (!(fabsf(r) <= 448.0f)) r = r > 0.0f ? 448.0f : (r < 0.0f ? -448.0f : 0.0f);   // inf / nan guard
+#pragma unroll
+      for (int t = 0; t < kNTerms; ++t) {
+        const uint8_t q = to_e4m3(r);
+        r -= from_e4m3(q);
+        packed[t] |= static_cast<uint32_t>(q) << (8 * i);
+      }
+    }
+#pragma unroll
+    for (int t = 0; t < kNTerms; ++t)
+      *reinterpret_cast<uint32_t*>(cq + (static_cast<size_t>(t) * rows_cap + row) * kI + kb * kBlock + lane * 4) =
+          packed[t];
+    if (lane == 0) c_scale[static_cast<size_t>(row) * kKB2 + kb] = scale;
+  }
+}
+
+__device__ __forceinline__ void swiglu_split_unit(const float* g1, size_t slab, int split, int row, int kb, int lane,
+                                                  uint8_t* cq, float* c_scale, int rows_cap) {
+  swiglu_split_blocks<1>(g1, slab, split, row, kb, lane, cq, c_scale, rows_cap);
 }
 
 __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
@@ -94,6 +110,45 @@ __device__ __forceinline__ void combine_unit(const float* o, size_t slab, int sp
   q.x = pack_bf16x2(acc.x, acc.y);
   q.y = pack_bf16x2(acc.z, acc.w);
   *reinterpret_cast<uint2*>(out_row + c * 4) = q;
+}
+
+// Weighted combine of a whole token by one 256-thread block: thread owns the float4 columns
+// tid, tid + 256, ... (7 of them), so every row contributes seven independent loads per thread.
+__device__ __forceinline__ void combine_token(const float* o, size_t slab, int split, int n_local, const int* rows,
+                                              const float* perm_weight, uint16_t* out_row) {
+  constexpr int kPer = kH / 4 / 256;   // 7
+  float4 acc[kPer];
+#pragma unroll
+  for (int x = 0; x < kPer; ++x) acc[x] = make_float4(0.f, 0.f, 0.f, 0.f);
+  for (int j = 0; j < n_local; ++j) {
+    const int row = rows[j];
+    const float w = perm_weight[row];
+    const float* p = o + static_cast<size_t>(row) * kH + threadIdx.x * 4;
+    float4 v[kPer];
+#pragma unroll
+    for (int x = 0; x < kPer; ++x) v[x] = __ldcg(reinterpret_cast<const float4*>(p + x * 1024));
+    for (int s = 1; s < split; ++s) {
+#pragma unroll
+      for (int x = 0; x < kPer; ++x) {
+        const float4 u = __ldcg(reinterpret_cast<const float4*>(p + s * slab + x * 1024));
+        v[x].x += u.x; v[x].y += u.y; v[x].z += u.z; v[x].w += u.w;
+      }
+    }
+#pragma unroll
+    for (int x = 0; x < kPer; ++x) {
+      acc[x].x = __fadd_rn(acc[x].x, __fmul_rn(v[x].x, w));
+      acc[x].y = __fadd_rn(acc[x].y, __fmul_rn(v[x].y, w));
+      acc[x].z = __fadd_rn(acc[x].z, __fmul_rn(v[x].z, w));
+      acc[x].w = __fadd_rn(acc[x].w, __fmul_rn(v[x].w, w));
+    }
+  }
+#pragma unroll
+  for (int x = 0; x < kPer; ++x) {
+    uint2 q;
+    q.x = pack_bf16x2(acc[x].x, acc[x].y);
+    q.y = pack_bf16x2(acc[x].z, acc[x].w);
+    *reinterpret_cast<uint2*>(out_row + threadIdx.x * 4 + x * 1024) = q;
+  }
 }
 
 }  // namespace moe

@@ -61,6 +61,7 @@ struct PermuteArgs {
   int* perm_token;              // [n_sel] token of each row
   float* perm_weight;           // [n_sel] combination weight of each row
   int* tok_rows;                // [T, 8] rows of a token in ascending local expert order
+  int* chunk_base;              // [ceil(T / 32), 32] first row of every (32-token chunk, expert); large T only
 };
 
 struct GatherArgs {

@@ -274,6 +274,7 @@ extern "C" int moe_fp8_block_scale_run(const float* routing_logits, const uint16
   int* perm_token = reinterpret_cast<int*>(ws + L.perm_token);
   float* perm_weight = reinterpret_cast<float*>(ws + L.perm_weight);
   int* tok_rows = reinterpret_cast<int*>(ws + L.tok_rows);
+  int* chunk_base = reinterpret_cast<int*>(ws + L.chunk_base);
   uint8_t* a_packed = ws + L.a_packed;
   float* a_scale_rows = reinterpret_cast<float*>(ws + L.a_scale_rows);
   float* g1 = reinterpret_cast<float*>(ws + L.g1);
@@ -324,11 +325,11 @@ extern "C" int moe_fp8_block_scale_run(const float* routing_logits, const uint16
   RouteArgs ra{routing_logits, routing_bias, T, local_expert_offset, routed_scaling_factor, topk_idx, topk_w,
                local_mask};
   PermuteArgs pa{T, local_expert_offset, n_tile, n_tile2, ctas, static_cast<int>(kps1), static_cast<int>(kps2), L.rows_cap, L.slab_rows, local_mask, topk_idx, topk_w,
-                 sched, perm_token, perm_weight, tok_rows};
+                 sched, perm_token, perm_weight, tok_rows, chunk_base};
   stage_mark(0, stream);
   launch_route_permute(ra, pa, stream);
   MOE_CUDA(cudaGetLastError());
-  g_launches += T <= 32 ? 1 : 2;
+  g_launches += T <= 32 ? 1 : T <= 1024 ? 2 : 3;
   stage_mark(1, stream);
 
   GatherArgs ga{sched, perm_token, hidden_states, hidden_states_scale, T, a_packed, a_scale_rows};

@@ -62,7 +62,7 @@ struct WorkspaceLayout {
   int T;
   int rows_cap;        // capacity in rows: 8*T rounded up to 128
   int slab_rows;       // rows of the fp32 slab areas: max(rows_cap, kMinSlabRows)
-  size_t sched, topk_idx, topk_w, local_mask, perm_token, perm_weight, tok_rows;
+  size_t sched, topk_idx, topk_w, local_mask, perm_token, perm_weight, tok_rows, chunk_base;
   size_t a_packed, a_scale_rows, g1, cq, c_scale, o;
   size_t total;
 };
@@ -89,6 +89,7 @@ inline WorkspaceLayout make_layout(int T) {
   L.perm_token = take(static_cast<size_t>(L.rows_cap) * 4);
   L.perm_weight = take(static_cast<size_t>(L.rows_cap) * 4);
   L.tok_rows = take(Tz * kTopK * 4);
+  L.chunk_base = take((Tz + 31) / 32 * kELocal * 4);   // first row of every (32-token chunk, expert)
   L.a_packed = take(static_cast<size_t>(L.rows_cap) * kH);
   L.a_scale_rows = take(static_cast<size_t>(L.rows_cap) * kKB1 * 4);
   L.g1 = take(static_cast<size_t>(L.slab_rows) * k2I * 4);

@@ -41,6 +41,44 @@ __device__ __forceinline__ void load_bias(const uint16_t* bias_bf16, float* bias
     bias_smem[i] = __uint_as_float(static_cast<uint32_t>(bias_bf16[i]) << 16);
 }
 
+constexpr int kPermuteFillInline = 1024;   // up to here the single permutation CTA also fills the rows
+
+// Rows of one 32-token chunk (lane = token).  `base`: lane = expert, the chunk's first row per expert;
+// returns the base of the next chunk.
+__device__ __forceinline__ int fill_chunk(const PermuteArgs& a, int c, int base, int lane) {
+  const uint32_t lt_mask = (1u << lane) - 1u;
+  const int t = c * 32 + lane;
+  const uint32_t m = t < a.T ? a.local_mask[t] : 0u;
+  int idx[kTopK];
+  float wgt[kTopK];
+  if (m) {
+#pragma unroll
+    for (int k = 0; k < kTopK; ++k) {
+      idx[k] = a.topk_idx[t * kTopK + k] - a.local_expert_offset;
+      wgt[k] = a.topk_w[t * kTopK + k];
+    }
+  }
+  int j = 0;                                  // rank of the expert among this token's local experts
+#pragma unroll
+  for (int le = 0; le < kELocal; ++le) {
+    const bool mine = (m >> le) & 1u;
+    const uint32_t b = __ballot_sync(0xFFFFFFFFu, mine);
+    const int first = __shfl_sync(0xFFFFFFFFu, base, le);
+    if (mine) {
+      const int row = first + __popc(b & lt_mask);
+      float w = 0.0f;
+#pragma unroll
+      for (int k = 0; k < kTopK; ++k) w = (idx[k] == le) ? wgt[k] : w;
+      a.perm_token[row] = t;
+      a.perm_weight[row] = w;
+      a.tok_rows[t * kTopK + j] = row;
+      ++j;
+    }
+    if (lane == le) base += __popc(b);
+  }
+  return base;
+}
+
 // Block-wide (1024 threads) histogram, scan, stable permutation and schedule.  Warp w owns
 // the contiguous token range [w * span, (w + 1) * span); inside a 32-token chunk lane = token.
 // Phase 1 counts, per warp and expert, the tokens that selected the expert; an exclusive
@@ -51,7 +89,6 @@ __device__ void permute_block(const PermuteArgs& a) {
   __shared__ int s_wcount[32][kELocal + 1];     // [warp][expert]: count, then first row (+1: no bank conflicts)
   const int lane = threadIdx.x & 31;
   const int warp = threadIdx.x >> 5;
-  const uint32_t lt_mask = (1u << lane) - 1u;
   const int chunks = (a.T + 31) / 32;
   const int span = (chunks + 31) / 32;          // chunks per warp
   const int c0 = warp * span, c1 = min(chunks, c0 + span);
@@ -117,37 +154,22 @@ __device__ void permute_block(const PermuteArgs& a) {
     }
   }
   __syncthreads();
-  // phase 2: fill.  `base` (lane = expert) is this warp's next free row of each expert.
+  // phase 2.  `base` (lane = expert) is this warp's next free row of each expert.  Small batches are
+  // filled here; for large ones the per-chunk bases are published and a multi-CTA kernel fills.
   int base = s_wcount[warp][lane];
+  const bool fill_here = a.T <= kPermuteFillInline;
   for (int c = c0; c < c1; ++c) {
-    const int t = c * 32 + lane;
-    const uint32_t m = t < a.T ? a.local_mask[t] : 0u;
-    int idx[kTopK];
-    float wgt[kTopK];
-    if (m) {
+    if (fill_here) {
+      base = fill_chunk(a, c, base, lane);
+    } else {
+      a.chunk_base[c * kELocal + lane] = base;
+      const int t = c * 32 + lane;
+      const uint32_t m = t < a.T ? a.local_mask[t] : 0u;
 #pragma unroll
-      for (int k = 0; k < kTopK; ++k) {
-        idx[k] = a.topk_idx[t * kTopK + k] - a.local_expert_offset;
-        wgt[k] = a.topk_w[t * kTopK + k];
+      for (int le = 0; le < kELocal; ++le) {
+        const int n = __popc(__ballot_sync(0xFFFFFFFFu, (m >> le) & 1u));
+        if (lane == le) base += n;
       }
-    }
-    int j = 0;                                  // rank of the expert among this token's local experts
-#pragma unroll
-    for (int le = 0; le < kELocal; ++le) {
-      const bool mine = (m >> le) & 1u;
-      const uint32_t b = __ballot_sync(0xFFFFFFFFu, mine);
-      const int first = __shfl_sync(0xFFFFFFFFu, base, le);
-      if (mine) {
-        const int row = first + __popc(b & lt_mask);
-        float w = 0.0f;
-#pragma unroll
-        for (int k = 0; k < kTopK; ++k) w = (idx[k] == le) ? wgt[k] : w;
-        a.perm_token[row] = t;
-        a.perm_weight[row] = w;
-        a.tok_rows[t * kTopK + j] = row;
-        ++j;
-      }
-      if (lane == le) base += __popc(b);
     }
   }
 }
@@ -169,6 +191,16 @@ __global__ void __launch_bounds__(1024) permute_kernel(PermuteArgs a) {
   griddep_launch_dependents();
   griddep_wait();
   permute_block(a);
+}
+
+// Large batches: one warp per 32-token chunk fills the rows from the published chunk bases.
+__global__ void __launch_bounds__(256) permute_fill_kernel(PermuteArgs a) {
+  griddep_launch_dependents();
+  griddep_wait();
+  const int lane = threadIdx.x & 31;
+  const int chunks = (a.T + 31) / 32;
+  for (int c = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); c < chunks; c += gridDim.x * (blockDim.x >> 5))
+    fill_chunk(a, c, a.chunk_base[c * kELocal + lane], lane);
 }
 
 // Small batches: routing and permutation in one single-CTA launch.
@@ -220,6 +252,10 @@ void launch_route_permute(const RouteArgs& r, const PermuteArgs& p, cudaStream_t
     const int grid = (r.T + 7) / 8 < 4 * kNumSMs ? (r.T + 7) / 8 : 4 * kNumSMs;
     launch_pdl(route_kernel, dim3(grid), dim3(256), 0, stream, r);
     launch_pdl(permute_kernel, dim3(1), dim3(1024), 0, stream, p);
+    if (r.T > kPermuteFillInline) {
+      const int chunks = (r.T + 31) / 32;
+      launch_pdl(permute_fill_kernel, dim3((chunks + 7) / 8), dim3(256), 0, stream, p);
+    }
   }
 }
 

@@ -12,7 +12,7 @@
 //
 // Limits and rules:
 //  * at most MOE_B200_STATIC_MAX_TOKENS tokens per call (larger T is rejected with
-//    MOE_B200_EINVAL); the array is ~150 KB and every GPU that loads the library
+//    MOE_B200_EINVAL); the array is ~160 KB and every GPU that loads the library
 //    holds it until the process exits;
 //  * the first call on a device looks the array's device address up
 //    (cudaGetSymbolAddress) with that device current; make that first call before
@@ -35,10 +35,11 @@ constexpr int kStaticMaxTokens = MOE_B200_STATIC_MAX_TOKENS;
 constexpr size_t kSchedBytes = (sizeof(MoeSched) + 1023) / 1024 * 1024;
 constexpr size_t kMaskBytes = static_cast<size_t>(kStaticMaxTokens) * 4;
 constexpr size_t kRowsBytes = static_cast<size_t>(kStaticMaxTokens) * kTopK * 4;
+constexpr size_t kChunkBytes = static_cast<size_t>(kStaticMaxTokens / 32) * kELocal * 4;
 
 // File-scope scratch.  In host code this name is only a handle for the runtime's
 // symbol lookup, never a pointer a kernel may be given.
-static __device__ __align__(256) unsigned char g_route_scratch[kSchedBytes + kMaskBytes + kRowsBytes];
+static __device__ __align__(256) unsigned char g_route_scratch[kSchedBytes + kMaskBytes + kRowsBytes + kChunkBytes];
 
 std::mutex g_static_mu;
 unsigned char* g_scratch_addr[16] = {};
@@ -79,11 +80,12 @@ extern "C" int moe_fp8_block_scale_route_static(const float* routing_logits, con
   MoeSched* sched = reinterpret_cast<MoeSched*>(scratch);
   uint32_t* local_mask = reinterpret_cast<uint32_t*>(scratch + kSchedBytes);
   int* tok_rows = reinterpret_cast<int*>(scratch + kSchedBytes + kMaskBytes);
+  int* chunk_base = reinterpret_cast<int*>(scratch + kSchedBytes + kMaskBytes + kRowsBytes);
   const int rows_cap = T * kTopK;
   RouteArgs ra{routing_logits, routing_bias, T, local_expert_offset, routed_scaling_factor, topk_idx, topk_w,
                local_mask};
   PermuteArgs pa{T, local_expert_offset, 128, 128, kNumSMs, 1, 1, rows_cap, rows_cap > kMinSlabRows ? rows_cap : kMinSlabRows,
-                 local_mask, topk_idx, topk_w, sched, perm_token, perm_weight, tok_rows};
+                 local_mask, topk_idx, topk_w, sched, perm_token, perm_weight, tok_rows, chunk_base};
   launch_route_permute(ra, pa, stream);
   if (cudaGetLastError() != cudaSuccess) return MOE_B200_ECUDA;
   if (cudaMemcpyAsync(expert_offsets, sched->offs, (kELocal + 1) * sizeof(int), cudaMemcpyDeviceToDevice, stream) !=

@@ -34,28 +34,24 @@ __global__ void __launch_bounds__(256) swiglu_split_kernel(SwigluArgs a) {
   const int n_sel = sc->n_sel, split = sc->split1;
   const size_t slab = static_cast<size_t>(sc->n_sel_pad) * k2I;
   const int lane = threadIdx.x & 31;
-  const long long nblk = static_cast<long long>(n_sel) * kKB2;
+  constexpr int kNB = 1;   // blocks per warp; more per warp measured slower (fewer warps in flight)
+  const long long nunit = static_cast<long long>(n_sel) * (kKB2 / kNB);
   const long long wstride = static_cast<long long>(gridDim.x) * (blockDim.x >> 5);
-  for (long long b = blockIdx.x * static_cast<long long>(blockDim.x >> 5) + (threadIdx.x >> 5); b < nblk; b += wstride)
-    swiglu_split_unit(a.g1, slab, split, static_cast<int>(b / kKB2), static_cast<int>(b % kKB2), lane, a.cq,
-                      a.c_scale, a.rows_cap);
+  for (long long b = blockIdx.x * static_cast<long long>(blockDim.x >> 5) + (threadIdx.x >> 5); b < nunit; b += wstride)
+    swiglu_split_blocks<kNB>(a.g1, slab, split, static_cast<int>(b / (kKB2 / kNB)),
+                             static_cast<int>(b % (kKB2 / kNB)) * kNB, lane, a.cq, a.c_scale, a.rows_cap);
 }
 
-// One thread per 4 output columns of a token.
+// One 256-thread block per token (grid-stride over tokens).
 __global__ void __launch_bounds__(256) combine_kernel(CombineArgs a) {
   griddep_launch_dependents();
   griddep_wait();
   const MoeSched* sc = a.sched;
   const int split = sc->split2;
   const size_t slab = static_cast<size_t>(sc->n_sel_pad) * kH;
-  constexpr int kVec = kH / 4;   // 1792 float4 per row
-  const long long total = static_cast<long long>(a.T) * kVec;
-  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
-       i += static_cast<long long>(gridDim.x) * blockDim.x) {
-    const int t = static_cast<int>(i / kVec), c = static_cast<int>(i % kVec);
-    combine_unit(a.o, slab, split, __popc(a.local_mask[t]), a.tok_rows + t * kTopK, a.perm_weight, c,
-                 a.out_bf16 + static_cast<size_t>(t) * kH);
-  }
+  for (int t = blockIdx.x; t < a.T; t += gridDim.x)
+    combine_token(a.o, slab, split, __popc(a.local_mask[t]), a.tok_rows + t * kTopK, a.perm_weight,
+                  a.out_bf16 + static_cast<size_t>(t) * kH);
 }
 
 }  // namespace
@@ -69,8 +65,7 @@ void launch_swiglu_split(const SwigluArgs& a, int T, cudaStream_t stream) {
 }
 
 void launch_combine(const CombineArgs& a, cudaStream_t stream) {
-  long long threads = static_cast<long long>(a.T) * (kH / 4);
-  long long blocks = (threads + 255) / 256;
+  long long blocks = a.T;
   if (blocks > 8 * kNumSMs) blocks = 8 * kNumSMs;
   if (blocks < 1) blocks = 1;
   launch_pdl(combine_kernel, dim3(static_cast<unsigned>(blocks)), dim3(256), 0, stream, a);

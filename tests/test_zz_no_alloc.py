@@ -33,7 +33,7 @@ def test_static_routing_matches_workspace_entry_point(pkg):
     dev = torch.device("cuda", 0)
     W = pkg.gen.make_shard_weights(0, dev, experts=[])       # routing does not read the weights
     rsf = 2.5
-    batches = [(300, 0, True, 0), (37, 3, False, 64)]        # big first: the second call sees its leftovers
+    batches = [(2500, 1, False, 32), (300, 0, True, 0), (37, 3, False, 64)]   # big first: later calls see leftovers
     tokens = [pkg.gen.make_tokens(T, seed, dev, skew) for T, seed, skew, _ in batches]
     got = [call_static(pkg, tok, T, off, rsf, dev) for tok, (T, _, _, off) in zip(tokens, batches)]
     for tok, (T, _, _, off), (idx, w, offs, ptok, pw) in zip(tokens, batches, got):
