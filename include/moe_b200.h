@@ -82,6 +82,37 @@ int moe_fp8_block_scale_route(const float* routing_logits, const uint16_t* routi
 int moe_fp8_block_scale_quantize_activations(const uint16_t* hidden_bf16, int T, uint8_t* hidden_states,
                                              float* hidden_states_scale, void* stream);
 
+/* The operator with a per-token destination: row t of the result is written to
+ * output_rows[t] (a device array of T device pointers, each 16-byte aligned and
+ * addressing 7168 bf16) instead of output + t * 7168.  The pointers may address a PEER
+ * GPU's memory (NVLink peer mapping): the expert-parallel layer uses this to let the
+ * combine stage of the shard operator store every row directly into the receive area
+ * of the rank that owns the token, i.e. the combine all-to-all happens inside the
+ * operator's last kernel.  No counterpart in the reference (it has no multi-rank code). */
+int moe_fp8_block_scale_run_rows(const float* routing_logits, const uint16_t* routing_bias,
+                                 const uint8_t* hidden_states, const float* hidden_states_scale,
+                                 const uint8_t* gemm1_weights, const float* gemm1_weights_scale,
+                                 const uint8_t* gemm2_weights, const float* gemm2_weights_scale,
+                                 int T, int local_expert_offset, float routed_scaling_factor,
+                                 uint16_t* const* output_rows, void* workspace, size_t workspace_bytes, void* stream);
+
+/* Expert-parallel dispatch over peer memory: for record r of segment s (records
+ * first_record .. first_record + count of rec_token, a token index each) copy the token's
+ * fp8 row, its 56 scales (gathered from the [56, T] layout) and its 256 logits to
+ * dst_hidden + k * 7168, dst_scale + k * 56, dst_logits + k * 256 (k = r - first_record),
+ * which may be peer-mapped memory of the rank that owns the segment's shard.  At most 8
+ * segments (one per shard).  No counterpart in the reference. */
+typedef struct moe_ep_segment {
+  int64_t first_record;
+  int64_t count;
+  uint8_t* dst_hidden;
+  float* dst_scale;
+  float* dst_logits;
+} moe_ep_segment;
+int moe_ep_dispatch_push(const uint8_t* hidden_states, const float* hidden_states_scale,
+                         const float* routing_logits, int T, const int64_t* rec_token, int n_records,
+                         const moe_ep_segment* segments, int n_segments, void* stream);
+
 /* Waits for `stream` and returns the error bits the kernels of the last call on
  * this workspace recorded (0 = none) in *status.  The reference checks no CUDA
  * return code at all (moe.cu:2729-2894); this is the replacement's error channel. */

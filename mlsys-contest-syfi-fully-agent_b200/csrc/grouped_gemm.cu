@@ -671,7 +671,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
           for (int i = blockIdx.x * kEpiThreads + etid; i < total; i += gridDim.x * kEpiThreads) {
             const int t = i / kVec, c = i % kVec;
             combine_unit(a.out, slab, split, __popc(a.local_mask[t]), a.tok_rows + t * kTopK, a.perm_weight, c,
-                         a.out_bf16 + static_cast<size_t>(t) * kH);
+                         a.out_rows ? a.out_rows[t] : a.out_bf16 + static_cast<size_t>(t) * kH);
           }
         }
       }

@@ -94,6 +94,7 @@ struct GemmArgs {
   int* perm_token; float* perm_weight; int* tok_rows;
   uint8_t* cq; float* c_scale;  // SwiGLU planes written by the fused GEMM1 tail
   uint16_t* out_bf16;           // final output written by the fused GEMM2 tail
+  uint16_t* const* out_rows;    // optional per-token destinations instead of out_bf16 (may be peer memory)
 };
 
 struct SwigluArgs {
@@ -112,6 +113,7 @@ struct CombineArgs {
   const float* perm_weight;
   uint16_t* out_bf16;           // [T, 7168]
   int T;
+  uint16_t* const* out_rows;    // optional: destination of every token's row (may be peer memory)
 };
 
 void launch_route_permute(const RouteArgs& r, const PermuteArgs& p, cudaStream_t stream);

@@ -245,16 +245,15 @@ extern "C" int moe_fp8_block_scale_layout(int T, moe_b200_layout* out) {
   return MOE_B200_OK;
 }
 
-extern "C" int moe_fp8_block_scale_run(const float* routing_logits, const uint16_t* routing_bias,
-                                       const uint8_t* hidden_states, const float* hidden_states_scale,
-                                       const uint8_t* gemm1_weights, const float* gemm1_weights_scale,
-                                       const uint8_t* gemm2_weights, const float* gemm2_weights_scale, int T,
-                                       int local_expert_offset, float routed_scaling_factor, uint16_t* output,
-                                       void* workspace, size_t workspace_bytes, void* stream_v) {
+static int run_impl(const float* routing_logits, const uint16_t* routing_bias, const uint8_t* hidden_states,
+                    const float* hidden_states_scale, const uint8_t* gemm1_weights, const float* gemm1_weights_scale,
+                    const uint8_t* gemm2_weights, const float* gemm2_weights_scale, int T, int local_expert_offset,
+                    float routed_scaling_factor, uint16_t* output, uint16_t* const* output_rows, void* workspace,
+                    size_t workspace_bytes, void* stream_v) {
   if (T < 0) return MOE_B200_EINVAL;
   if (T == 0) return MOE_B200_OK;
   if (!routing_logits || !routing_bias || !hidden_states || !hidden_states_scale || !gemm1_weights ||
-      !gemm1_weights_scale || !gemm2_weights || !gemm2_weights_scale || !output || !workspace)
+      !gemm1_weights_scale || !gemm2_weights || !gemm2_weights_scale || (!output && !output_rows) || !workspace)
     return MOE_B200_EINVAL;
   if (!aligned16(hidden_states) || !aligned16(gemm1_weights) || !aligned16(gemm2_weights) || !aligned16(output) ||
       (reinterpret_cast<uintptr_t>(workspace) & 1023u) != 0)
@@ -310,7 +309,7 @@ extern "C" int moe_fp8_block_scale_run(const float* routing_logits, const uint16
     fa.call_tag = call_counter.fetch_add(2654435761u) | 1u;
     fa.topk_idx = topk_idx; fa.topk_w = topk_w; fa.local_mask = local_mask;
     fa.perm_token = perm_token; fa.perm_weight = perm_weight; fa.tok_rows = tok_rows;
-    fa.cq = cq; fa.c_scale = c_scale; fa.out_bf16 = output;
+    fa.cq = cq; fa.c_scale = c_scale; fa.out_bf16 = output; fa.out_rows = output_rows;
     stage_mark(0, stream); stage_mark(1, stream); stage_mark(2, stream);
     if ((rc = launch_fused_gemm(1, tm_w13, tm_h, fa, ctas, stream))) { g_last_cuda_error = rc; return MOE_B200_ECUDA; }
     stage_mark(3, stream); stage_mark(4, stream);
@@ -362,12 +361,37 @@ extern "C" int moe_fp8_block_scale_run(const float* routing_logits, const uint16
   g_launches += 1;
   stage_mark(5, stream);
 
-  CombineArgs ca{sched, o, local_mask, tok_rows, perm_weight, output, T};
+  CombineArgs ca{sched, o, local_mask, tok_rows, perm_weight, output, T, output_rows};
   launch_combine(ca, stream);
   MOE_CUDA(cudaGetLastError());
   g_launches += 1;
   stage_mark(6, stream);
   return MOE_B200_OK;
+}
+
+extern "C" int moe_fp8_block_scale_run(const float* routing_logits, const uint16_t* routing_bias,
+                                       const uint8_t* hidden_states, const float* hidden_states_scale,
+                                       const uint8_t* gemm1_weights, const float* gemm1_weights_scale,
+                                       const uint8_t* gemm2_weights, const float* gemm2_weights_scale, int T,
+                                       int local_expert_offset, float routed_scaling_factor, uint16_t* output,
+                                       void* workspace, size_t workspace_bytes, void* stream_v) {
+  if (T > 0 && !output) return MOE_B200_EINVAL;
+  return run_impl(routing_logits, routing_bias, hidden_states, hidden_states_scale, gemm1_weights, gemm1_weights_scale,
+                  gemm2_weights, gemm2_weights_scale, T, local_expert_offset, routed_scaling_factor, output, nullptr,
+                  workspace, workspace_bytes, stream_v);
+}
+
+extern "C" int moe_fp8_block_scale_run_rows(const float* routing_logits, const uint16_t* routing_bias,
+                                            const uint8_t* hidden_states, const float* hidden_states_scale,
+                                            const uint8_t* gemm1_weights, const float* gemm1_weights_scale,
+                                            const uint8_t* gemm2_weights, const float* gemm2_weights_scale, int T,
+                                            int local_expert_offset, float routed_scaling_factor,
+                                            uint16_t* const* output_rows, void* workspace, size_t workspace_bytes,
+                                            void* stream_v) {
+  if (T > 0 && !output_rows) return MOE_B200_EINVAL;
+  return run_impl(routing_logits, routing_bias, hidden_states, hidden_states_scale, gemm1_weights, gemm1_weights_scale,
+                  gemm2_weights, gemm2_weights_scale, T, local_expert_offset, routed_scaling_factor, nullptr,
+                  output_rows, workspace, workspace_bytes, stream_v);
 }
 
 extern "C" int moe_fp8_block_scale_run_host(const float* routing_logits_host, const uint16_t* routing_bias_host,

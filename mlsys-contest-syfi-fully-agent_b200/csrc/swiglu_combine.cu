@@ -51,7 +51,7 @@ __global__ void __launch_bounds__(256) combine_kernel(CombineArgs a) {
   const size_t slab = static_cast<size_t>(sc->n_sel_pad) * kH;
   for (int t = blockIdx.x; t < a.T; t += gridDim.x)
     combine_token(a.o, slab, split, __popc(a.local_mask[t]), a.tok_rows + t * kTopK, a.perm_weight,
-                  a.out_bf16 + static_cast<size_t>(t) * kH);
+                  a.out_rows ? a.out_rows[t] : a.out_bf16 + static_cast<size_t>(t) * kH);
 }
 
 }  // namespace

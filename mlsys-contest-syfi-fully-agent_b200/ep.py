@@ -21,6 +21,16 @@ This module adds the one exchange pair that turns eight shards into the layer:
 Counts are exchanged with one small all-gather and read on the host (the split
 sizes of ``all_to_all_single`` are host integers).  No collective other than these.
 
+Two transports.  ``"nccl"``: the exchange is ``all_to_all_single`` and the gather / pack /
+accumulate steps are torch index operations.  ``"p2p"``: every rank owns a symmetric buffer
+(torch symmetric memory: the same allocation mapped into every peer over NVLink); the
+dispatch is ONE kernel that gathers, packs and stores each record straight into the owner's
+receive area (``moe_ep_dispatch_push``), and the combine happens inside the shard operator's
+last kernel, which writes every result row directly into the source rank's receive area
+(``moe_fp8_block_scale_run_rows`` with peer destinations).  Between the phases the ranks meet
+at the symmetric-memory barrier.  Plain peer stores only: no multicast, no TMA on peer memory,
+and no kernel ever waits on a peer.
+
 ``local_op`` and ``route_fn`` are injectable so that the host-side logic can be
 tested with gloo on CPU ranks; the defaults are the CUDA operator and fail loudly
 without the compiled library.
@@ -89,12 +99,56 @@ def _all_to_all(out: torch.Tensor, inp: torch.Tensor, out_splits, in_splits, wor
     return out
 
 
+class PeerExchange:
+    """Symmetric receive areas of the p2p transport and their peer addresses.
+
+    Layout (same on every rank): fp8 rows | block scales | logits for the records this rank
+    receives, then the bf16 result rows that come back for the records it sent."""
+
+    def __init__(self, rank: int, world: int, group, device, max_recv_rows: int, max_send_rows: int, n_logits: int):
+        self.rank, self.world = rank, world
+        al = lambda x: (x + 255) // 256 * 256
+        self.off_h = 0
+        self.off_s = al(max_recv_rows * H)
+        self.off_l = self.off_s + al(max_recv_rows * KB * 4)
+        self.off_back = self.off_l + al(max_recv_rows * n_logits * 4)
+        total = self.off_back + al(max_send_rows * H * 2)
+        self.max_recv_rows, self.max_send_rows, self.n_logits = max_recv_rows, max_send_rows, n_logits
+        if world > 1:
+            import torch.distributed._symmetric_memory as symm
+            self.buf = symm.empty(total, dtype=torch.uint8, device=device)
+            grp = group if group is not None else dist.group.WORLD
+            self.handle = symm.rendezvous(self.buf, group=grp.group_name)
+            self.ptrs = [int(p) for p in self.handle.buffer_ptrs]
+        else:
+            self.buf = torch.empty(total, dtype=torch.uint8, device=device)
+            self.handle = None
+            self.ptrs = [self.buf.data_ptr()]
+
+    def barrier(self):
+        if self.handle is not None:
+            self.handle.barrier()
+
+    def recv_views(self, n: int):
+        h = self.buf[self.off_h:self.off_h + n * H].view(n, H)
+        s = self.buf[self.off_s:self.off_s + n * KB * 4].view(torch.float32).view(n, KB)
+        l = self.buf[self.off_l:self.off_l + n * self.n_logits * 4].view(torch.float32).view(n, self.n_logits)
+        return h, s, l
+
+    def back_view(self, n: int):
+        return self.buf[self.off_back:self.off_back + n * H * 2].view(torch.bfloat16).view(n, H)
+
+
 class ExpertParallelMoE:
     """The layer.  ``shard_weights[i]`` are the four weight tensors of the i-th shard this
     rank owns (``shards_of_rank(rank, world)`` order)."""
 
     def __init__(self, shard_weights: Sequence, rank: int = 0, world: int = 1, group=None,
-                 local_op: Optional[Callable] = None, route_fn: Optional[Callable] = None):
+                 local_op: Optional[Callable] = None, route_fn: Optional[Callable] = None, transport: str = "nccl"):
+        if transport not in ("nccl", "p2p"):
+            raise ValueError("transport must be 'nccl' or 'p2p'")
+        self.transport = transport
+        self._px: Optional[PeerExchange] = None
         self.rank, self.world, self.group = rank, world, group
         self.shards = shards_of_rank(rank, world)
         if len(shard_weights) != len(self.shards):
@@ -117,6 +171,9 @@ class ExpertParallelMoE:
         topk_idx = self.route_fn(routing_logits, routing_bias, routed_scaling_factor)
         plan = build_plan(topk_idx, world, rank, self.group)
         self.last_plan = plan
+        if self.transport == "p2p":
+            return self._forward_p2p(plan, routing_logits, routing_bias, hidden_states, hidden_states_scale,
+                                     routed_scaling_factor)
         order = plan.send_order
         n_send, n_recv = int(order.numel()), sum(plan.recv_counts)
 
@@ -174,6 +231,88 @@ class ExpertParallelMoE:
                 acc.index_add_(0, toks, back[pos:pos + n].to(torch.float32))
             pos += n
         return acc.to(torch.bfloat16)
+
+
+def _forward_p2p(self, plan: DispatchPlan, routing_logits, routing_bias, hidden_states, hidden_states_scale,
+                 routed_scaling_factor: float) -> torch.Tensor:
+    """p2p transport: dispatch by one push kernel, combine inside the shard operator (see module docstring)."""
+    import ctypes
+
+    from . import loader, op
+    world, rank = self.world, self.rank
+    T = routing_logits.shape[0]
+    dev = hidden_states.device
+    n_logits = routing_logits.shape[1]
+    per = N_SHARDS // world
+    if self._px is None:
+        # capacities for equal token counts per rank: every token of every rank may select each of my shards
+        self._px = PeerExchange(rank, world, self.group, dev, max(1, T * world * per), max(1, T * N_SHARDS), n_logits)
+    px = self._px
+    counts = plan.counts                                    # [world, 8] host
+    totals = counts.sum(dim=0)                              # records per shard over all sources
+    n_send = int(counts[rank].sum())
+    n_recv = int(sum(int(totals[s]) for s in self.shards))
+    if n_recv > px.max_recv_rows or n_send > px.max_send_rows:
+        raise RuntimeError("symmetric receive area too small for this batch")
+
+    def recv_row_base(d: int, s: int, src: int) -> int:
+        """First row, in rank d's receive area, of the records that `src` sends for shard s (shard-major)."""
+        first = d * per
+        return int(totals[first:s].sum()) + int(counts[:src, s].sum())
+
+    px.barrier()                                            # peers have finished reading the previous call's areas
+    segs = (loader.EpSegment * N_SHARDS)()
+    nseg, first = 0, 0
+    for s in range(N_SHARDS):
+        n = int(counts[rank, s])
+        if n:
+            d = owner_of_shard(s, world)
+            row = recv_row_base(d, s, rank)
+            segs[nseg] = loader.EpSegment(first, n, px.ptrs[d] + px.off_h + row * H,
+                                          px.ptrs[d] + px.off_s + row * KB * 4,
+                                          px.ptrs[d] + px.off_l + row * n_logits * 4)
+            nseg += 1
+        first += n
+    if n_send:
+        with torch.cuda.device(dev):
+            loader.check(loader.lib.moe_ep_dispatch_push(
+                hidden_states.data_ptr(), hidden_states_scale.data_ptr(), routing_logits.data_ptr(), int(T),
+                plan.send_order.data_ptr(), n_send, segs, nseg, torch.cuda.current_stream(dev).cuda_stream))
+    px.barrier()                                            # every record has landed
+
+    recv_h, recv_s, recv_l = px.recv_views(n_recv)
+    row0 = 0
+    for j, s in enumerate(self.shards):
+        n_s = int(totals[s])
+        if n_s:
+            rows = slice(row0, row0 + n_s)
+            # destination of every result row: the position of its record in the source rank's send order
+            ptrs = []
+            for src in range(world):
+                n = int(counts[src, s])
+                if n:
+                    base = px.ptrs[src] + px.off_back + int(counts[src, :s].sum()) * H * 2
+                    ptrs.append(base + torch.arange(n, device=dev, dtype=torch.int64) * (H * 2))
+            w = self.shard_weights[j]
+            op.run_rows(recv_l[rows], routing_bias, recv_h[rows].view(torch.float8_e4m3fn),
+                        recv_s[rows].t().contiguous(), w.gemm1_weights, w.gemm1_weights_scale, w.gemm2_weights,
+                        w.gemm2_weights_scale, E_LOCAL * s, routed_scaling_factor, torch.cat(ptrs))
+        row0 += n_s
+    px.barrier()                                            # every result row has landed at its source
+
+    back = px.back_view(n_send)
+    acc = torch.zeros((T, H), dtype=torch.float32, device=dev)
+    pos = 0
+    for s in range(N_SHARDS):
+        toks = plan.token_lists[s]
+        n = int(toks.numel())
+        if n:
+            acc.index_add_(0, toks, back[pos:pos + n].to(torch.float32))
+        pos += n
+    return acc.to(torch.bfloat16)
+
+
+ExpertParallelMoE._forward_p2p = _forward_p2p
 
 
 def layer_reference(shard_run: Callable[[int], torch.Tensor]) -> torch.Tensor:

@@ -29,6 +29,8 @@ EXPORTS = [
     "moe_fp8_block_scale_route_static",
     "moe_fp8_block_scale_route",
     "moe_fp8_block_scale_quantize_activations",
+    "moe_fp8_block_scale_run_rows",
+    "moe_ep_dispatch_push",
 ]
 STATIC_MAX_TOKENS = 4096
 STAGES = ("route_permute", "gather", "gemm1", "swiglu_split", "gemm2", "combine")
@@ -47,6 +49,11 @@ class Sched(ctypes.Structure):
                                               "split1", "split2", "items1", "items2")] + \
                [("bar1", ctypes.c_uint32 * 2), ("bar2", ctypes.c_uint32 * 2), ("n_tile2", ctypes.c_int32), ("pad_", ctypes.c_int32 * 1), ("counts", ctypes.c_int32 * 32), ("offs", ctypes.c_int32 * 33),
                 ("tile_prefix", ctypes.c_int32 * 33), ("tile_prefix2", ctypes.c_int32 * 33)]
+
+
+class EpSegment(ctypes.Structure):
+    _fields_ = [("first_record", ctypes.c_int64), ("count", ctypes.c_int64), ("dst_hidden", ctypes.c_void_p),
+                ("dst_scale", ctypes.c_void_p), ("dst_logits", ctypes.c_void_p)]
 
 
 class MoeLibraryError(RuntimeError):
@@ -83,6 +90,10 @@ def _load() -> ctypes.CDLL:
     lib.moe_fp8_block_scale_route.argtypes = [vp, vp, i32, i32, f32, vp, vp, vp, vp]
     lib.moe_fp8_block_scale_quantize_activations.restype = i32
     lib.moe_fp8_block_scale_quantize_activations.argtypes = [vp, i32, vp, vp, vp]
+    lib.moe_fp8_block_scale_run_rows.restype = i32
+    lib.moe_fp8_block_scale_run_rows.argtypes = run_args
+    lib.moe_ep_dispatch_push.restype = i32
+    lib.moe_ep_dispatch_push.argtypes = [vp, vp, vp, i32, vp, i32, ctypes.POINTER(EpSegment), i32, vp]
     lib.moe_fp8_block_scale_launch_count.restype = ctypes.c_longlong
     lib.moe_fp8_block_scale_launch_count.argtypes = []
     lib.moe_fp8_block_scale_set_profiling.restype = i32

@@ -121,6 +121,30 @@ def run(routing_logits: torch.Tensor, routing_bias: torch.Tensor, hidden_states:
     return output
 
 
+def run_rows(routing_logits, routing_bias, hidden_states, hidden_states_scale, gemm1_weights, gemm1_weights_scale,
+             gemm2_weights, gemm2_weights_scale, local_expert_offset: int, routed_scaling_factor: float,
+             output_rows: torch.Tensor, workspace: Optional[Workspace] = None) -> None:
+    """The operator with a per-token destination: ``output_rows`` is an int64 CUDA tensor of T device
+    addresses (16-byte aligned, 7168 bf16 each; peer-mapped memory allowed) that row t is written to."""
+    T = routing_logits.shape[0]
+    dummy = torch.empty((T, H), dtype=torch.bfloat16, device="meta")
+    _check(output_rows.dtype == torch.int64 and output_rows.numel() == T and output_rows.is_cuda and
+           output_rows.is_contiguous(), "output_rows must be a contiguous CUDA int64 tensor of T addresses")
+    del dummy
+    if T == 0:
+        return
+    dev = hidden_states.device
+    ws = (workspace or _default_workspace(dev)).reserve(T)
+    with torch.cuda.device(dev):
+        stream = torch.cuda.current_stream(dev).cuda_stream
+        rc = loader.lib.moe_fp8_block_scale_run_rows(
+            routing_logits.data_ptr(), routing_bias.data_ptr(), hidden_states.data_ptr(),
+            hidden_states_scale.data_ptr(), gemm1_weights.data_ptr(), gemm1_weights_scale.data_ptr(),
+            gemm2_weights.data_ptr(), gemm2_weights_scale.data_ptr(), int(T), int(local_expert_offset),
+            float(routed_scaling_factor), output_rows.data_ptr(), ws.ptr, ws.nbytes, stream)
+    loader.check(rc)
+
+
 def run_host(routing_logits, routing_bias, hidden_states, hidden_states_scale, gemm1_weights, gemm1_weights_scale,
              gemm2_weights, gemm2_weights_scale, local_expert_offset: int, routed_scaling_factor: float,
              output: torch.Tensor, workspace: Optional[Workspace] = None) -> torch.Tensor:

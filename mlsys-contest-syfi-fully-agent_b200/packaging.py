@@ -22,7 +22,7 @@ AUTHOR = "b200-native"
 ENTRY_POINT = "tvm_ffi_shim.cu::run"
 
 SOURCE_FILES = ["tvm_ffi_shim.cu", "launcher.cu", "route_permute.cu", "grouped_gemm.cu", "swiglu_combine.cu",
-                "static_entry.cu", "quantize.cu", "kernels.h", "moe_layout.h", "ptx.cuh", "route_device.cuh",
+                "static_entry.cu", "quantize.cu", "ep_push.cu", "kernels.h", "moe_layout.h", "ptx.cuh", "route_device.cuh",
                 "epilogue_device.cuh"]
 
 

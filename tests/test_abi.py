@@ -20,7 +20,7 @@ def loader(pkg):
 def declared_functions():
     text = open(os.path.join(ROOT, "include", "moe_b200.h")).read()
     text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
-    return sorted(set(re.findall(r"\b(moe_fp8_block_scale_\w+)\s*\(", text)))
+    return sorted(set(re.findall(r"\b(moe_(?:fp8_block_scale|ep)_\w+)\s*\(", text)))
 
 
 def test_header_and_library_agree(loader):

@@ -20,13 +20,13 @@ RSF = 2.5
 T_TOTAL = 64
 
 
-def _layer_case(pkg, rank, world, dev):
+def _layer_case(pkg, rank, world, dev, transport="nccl"):
     ep, gen = pkg.ep, pkg.gen
     torch.backends.cuda.matmul.allow_tf32 = False
     tok = gen.make_tokens(T_TOTAL, 0, dev)
     shards = ep.shards_of_rank(rank, world)
     weights = {s: gen.make_shard_weights(1000 + s, dev) for s in shards}
-    layer = ep.ExpertParallelMoE([weights[s] for s in shards], rank, world)
+    layer = ep.ExpertParallelMoE([weights[s] for s in shards], rank, world, transport=transport)
     T = T_TOTAL // world
     sl = slice(rank * T, (rank + 1) * T)
     out = layer.forward(tok.routing_logits[sl].contiguous(), tok.routing_bias, tok.hidden_states[sl].contiguous(),
@@ -49,6 +49,7 @@ def _layer_case(pkg, rank, world, dev):
     idx, _ = moe_oracle.routing(tok.routing_logits[sl], tok.routing_bias, RSF)
     want = sum(len(set((r // 32).tolist())) for r in idx.cpu())
     assert sum(layer.last_plan.send_counts) == want
+    m["digest"] = pkg.gen.digest(out)
     return m
 
 
@@ -60,7 +61,10 @@ def _check(m):
 
 def test_layer_on_one_gpu(pkg):
     dev = torch.device("cuda", 0)
-    _check(_layer_case(pkg, 0, 1, dev))
+    a = _layer_case(pkg, 0, 1, dev)
+    _check(a)
+    b = _layer_case(pkg, 0, 1, dev, transport="p2p")      # world size 1: the push / row-pointer kernels, local memory
+    assert a["digest"] == b["digest"], "p2p transport differs from the NCCL transport"
 
 
 def _worker(rank, world, port, ret):
@@ -72,7 +76,10 @@ def _worker(rank, world, port, ret):
     torch.cuda.set_device(dev)
     dist.init_process_group("nccl", init_method=f"tcp://127.0.0.1:{port}", rank=rank, world_size=world, device_id=dev)
     try:
-        ret[rank] = _layer_case(load_package(), rank, world, dev)
+        a = _layer_case(load_package(), rank, world, dev)
+        b = _layer_case(load_package(), rank, world, dev, transport="p2p")
+        a["p2p_same_bits"] = a["digest"] == b["digest"]
+        ret[rank] = a
     finally:
         dist.destroy_process_group()
 
@@ -87,3 +94,4 @@ def test_layer_on_two_gpus():
     mp.spawn(_worker, args=(2, port, ret), nprocs=2, join=True)
     for r in range(2):
         _check(ret[r])
+        assert ret[r]["p2p_same_bits"], "peer-memory transport differs from the NCCL transport"
