@@ -353,40 +353,48 @@ def bench_main(args):
     hscale = tok_all.hidden_states_scale[:, sl].contiguous()
     bias = tok_all.routing_bias
     del tok_all
-    layer = ExpertParallelMoE(weights, rank, world)
-
-    def step():
-        return layer.forward(logits, bias, hidden, hscale, rsf)
+    transports = [os.environ.get("MOE_B200_EP_TRANSPORT", "p2p")]
+    if transports[0] == "p2p":
+        transports.append("nccl")          # also timed, reported beside the headline
 
     def sync():
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize()
 
-    for _ in range(max(args.warmup, 3)):
-        step()
-    sync()
-    l0 = loader.launch_count()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for _ in range(args.steps):
-        out = step()
-    e1.record()
-    sync()
-    ms = torch.tensor([e0.elapsed_time(e1)], device=dev)
-    n_rows = torch.tensor([float(sum(layer.last_plan.recv_counts))], device=dev)
-    if world > 1:
-        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+    results = {}
+    for tr in transports:
+        layer = ExpertParallelMoE(weights, rank, world, transport=tr)
+
+        def step():
+            return layer.forward(logits, bias, hidden, hscale, rsf)
+
+        for _ in range(max(args.warmup, 3)):
+            step()
+        sync()
+        l0 = loader.launch_count()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(args.steps):
+            out = step()
+        e1.record()
+        sync()
+        ms = torch.tensor([e0.elapsed_time(e1)], device=dev)
+        n_rows = torch.tensor([float(sum(layer.last_plan.recv_counts))], device=dev)
         rows_max = n_rows.clone()
-        dist.all_reduce(rows_max, op=dist.ReduceOp.MAX)
-        dist.all_reduce(n_rows, op=dist.ReduceOp.SUM)
-    else:
-        rows_max = n_rows
-    launches = loader.launch_count() - l0
+        if world > 1:
+            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+            dist.all_reduce(rows_max, op=dist.ReduceOp.MAX)
+            dist.all_reduce(n_rows, op=dist.ReduceOp.SUM)
+        results[tr] = dict(ms_step=float(ms) / args.steps, launches=loader.launch_count() - l0,
+                           rows=float(n_rows), rows_max=float(rows_max), digest=gen.digest(out))
+        del layer
     assert op.kernel_status(device=dev) == 0
+    if len(results) == 2:
+        assert results["p2p"]["digest"] == results["nccl"]["digest"], "transports disagree"
     if rank == 0:
-        ms_step = float(ms) / args.steps
-        total_rows = float(n_rows)
+        head = results[transports[0]]
+        ms_step, total_rows, rows_max = head["ms_step"], head["rows"], head["rows_max"]
         print(json.dumps({
             "metric": "moe_tokens_per_second", "value": T_total / (ms_step * 1e-3), "unit": "tokens/s",
             "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_step,
@@ -394,13 +402,20 @@ def bench_main(args):
             "data": "synthetic",
             "config": {"workload": "ep_layer_t16384", "T": T_total, "tokens_per_rank": T, "experts": 256,
                        "shards_per_rank": len(shards), "token_seed": 0, "weight_seeds": "1000 + shard",
-                       "dispatch": "NCCL all_to_all_single (fp8 row + scales + logits per (token, shard))",
-                       "combine": "NCCL all_to_all_single (bf16 row per (token, shard))",
+                       "transport": transports[0],
+                       "dispatch": "one push kernel into the owner's symmetric receive area over NVLink "
+                                   "(fp8 row + scales + logits per (token, shard))" if transports[0] == "p2p"
+                                   else "NCCL all_to_all_single",
+                       "combine": "written by the shard operator's last kernel into the source rank's receive area "
+                                  "(bf16 row per (token, shard))" if transports[0] == "p2p" else "NCCL all_to_all_single",
                        "l2": "per-rank weights (>= 1.4 GB) exceed L2", "records_total": total_rows,
-                       "load_balance_bound": total_rows / world / float(rows_max)},
-            "gpu_launches": int(launches),
+                       "load_balance_bound": total_rows / world / rows_max},
+            "gpu_launches": int(head["launches"]),
+            "nccl_transport": ({"ms_per_step": results["nccl"]["ms_step"],
+                                "tokens_per_s": T_total / (results["nccl"]["ms_step"] * 1e-3)}
+                               if "nccl" in results and transports[0] != "nccl" else None),
+            "fp8_tflops_per_gpu": total_rows and (T_total * 8 * 88080384 / world) / (ms_step * 1e-3) / 1e12,
             "e2e": None, "roofline": None, "cpu_baseline": None,
-            "fp8_tflops_per_gpu": None,
         }))
     if world > 1:
         dist.destroy_process_group()
