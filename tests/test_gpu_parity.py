@@ -246,3 +246,36 @@ def test_activation_quantisation_is_bit_exact(pkg, dev, T):
     q_ref, s_ref = pkg.gen.quant_1x128(x.to(torch.float32))
     assert torch.equal(s, s_ref.t().contiguous())
     assert torch.equal(q.view(torch.uint8), q_ref.view(torch.uint8))
+
+
+def test_routing_randomised_against_oracle(pkg, dev):
+    """Routing alone (moe_fp8_block_scale_route) on many random batches, bias scales and shard
+    offsets: selected expert sets and the local-expert mask bit for bit, weights to 1e-6.
+    Includes biases large enough to pin whole groups and logits with a narrow spread
+    (many near-equal scores)."""
+    g = torch.Generator().manual_seed(1234)
+    total = 0
+    for case in range(24):
+        T = int(torch.randint(1, 700, (1,), generator=g))
+        seed = int(torch.randint(0, 10 ** 6, (1,), generator=g))
+        offset = 32 * int(torch.randint(0, 8, (1,), generator=g))
+        tok = pkg.gen.make_tokens(T, seed, dev, skew=(case % 5 == 0))
+        logits = tok.routing_logits * (0.05 if case % 3 == 0 else 1.0 if case % 3 == 1 else 4.0)
+        bias = (tok.routing_bias.float() * (1.0 if case % 2 == 0 else 8.0)).to(torch.bfloat16)
+        idx, w, mask = pkg.op.route(logits.contiguous(), bias, offset, RSF)
+        ref_idx, ref_w = moe_oracle.routing(logits, bias, RSF)
+        same = moe_oracle.selection_sets_equal(idx, ref_idx)
+        if not bool(same.all()):
+            gap_g, gap_e = moe_oracle.selection_margins(logits, bias)
+            bad = (~same).nonzero().squeeze(1)
+            # a mismatch is acceptable only on an exact tie, which torch.topk may break either way
+            assert bool(((gap_g[bad.to(dev)] == 0) | (gap_e[bad.to(dev)] == 0)).all()), \
+                f"selection differs on tokens {bad.tolist()} without a tie"
+        ok = same.to(dev)
+        torch.testing.assert_close(w[ok], ref_w.gather(1, idx.long())[ok], rtol=1e-6, atol=1e-9)
+        local = ((ref_idx >= offset) & (ref_idx < offset + 32))
+        want_mask = torch.where(local, torch.ones_like(ref_idx) << (ref_idx - offset).clamp(0, 31),
+                                torch.zeros_like(ref_idx)).sum(dim=1)
+        assert torch.equal(mask.long()[ok] & 0xFFFFFFFF, want_mask[ok] & 0xFFFFFFFF)
+        total += T
+    assert total > 1000
