@@ -187,6 +187,78 @@ __global__ void __launch_bounds__(256) route_kernel(RouteArgs a) {
   route_tokens_strided(a, bias_smem, blockIdx.x * warps + (threadIdx.x >> 5), gridDim.x * warps, threadIdx.x & 31);
 }
 
+// One 256-thread CTA per token (thread = expert, warp = routing group): sigmoid + bias, the group's
+// two best by two warp reductions, then every kept expert counts the kept experts that beat it; the
+// eight with rank < 8 are the selection in descending order.  Same arithmetic and tie rules as
+// route_token, a third of its latency; used while there are at most a couple of tokens per CTA.
+__global__ void __launch_bounds__(256) route_block_kernel(RouteArgs a) {
+  __shared__ __align__(16) uint32_t keys[kEGlobal];
+  __shared__ float gscore[kNGroup];
+  __shared__ int selidx[kTopK];
+  __shared__ float sels[kTopK];
+  griddep_launch_dependents();
+  griddep_wait();
+  const int e = threadIdx.x, lane = e & 31, warp = e >> 5;
+  const float bias_e = __uint_as_float(static_cast<uint32_t>(a.bias_bf16[e]) << 16);
+  for (int t = blockIdx.x; t < a.T; t += gridDim.x) {
+    const float s_e = 1.0f / (1.0f + expf(-a.logits[static_cast<size_t>(t) * kEGlobal + e]));
+    const uint32_t key_e = order_key(s_e + bias_e);
+    keys[e] = key_e;
+    const uint32_t k1 = __reduce_max_sync(0xFFFFFFFFu, key_e);
+    const int first = __ffs(__ballot_sync(0xFFFFFFFFu, key_e == k1)) - 1;
+    const uint32_t k2 = __reduce_max_sync(0xFFFFFFFFu, lane == first ? 0u : key_e);
+    const uint32_t u1 = (k1 & 0x80000000u) ? (k1 & 0x7FFFFFFFu) : ~k1;
+    const uint32_t u2 = (k2 & 0x80000000u) ? (k2 & 0x7FFFFFFFu) : ~k2;
+    if (lane == 0) gscore[warp] = __uint_as_float(u1) + __uint_as_float(u2);
+    __syncthreads();
+    uint32_t keep = 0;
+#pragma unroll
+    for (int g = 0; g < kNGroup; ++g) {
+      int rank = 0;
+#pragma unroll
+      for (int h = 0; h < kNGroup; ++h) rank += (gscore[h] > gscore[g]) || (gscore[h] == gscore[g] && h < g);
+      keep |= (rank < kTopKGroup ? 1u : 0u) << g;
+    }
+    if ((keep >> warp) & 1u) {
+      int rank = 0;
+      for (int g = 0; g < kNGroup; ++g) {
+        if (!((keep >> g) & 1u)) continue;
+        const uint4* kv = reinterpret_cast<const uint4*>(keys + g * 32);
+#pragma unroll
+        for (int c = 0; c < 8; ++c) {
+          const uint4 k = kv[c];
+          const int j = g * 32 + c * 4;
+          rank += (k.x > key_e) || (k.x == key_e && j + 0 < e);
+          rank += (k.y > key_e) || (k.y == key_e && j + 1 < e);
+          rank += (k.z > key_e) || (k.z == key_e && j + 2 < e);
+          rank += (k.w > key_e) || (k.w == key_e && j + 3 < e);
+        }
+      }
+      if (rank < kTopK) { selidx[rank] = e; sels[rank] = s_e; }
+    }
+    __syncthreads();
+    if (warp == 0) {
+      const float sv = lane < kTopK ? sels[lane] : 0.0f;
+      float sum = 0.0f;
+#pragma unroll
+      for (int k = 0; k < kTopK; ++k) sum += __shfl_sync(0xFFFFFFFFu, sv, k);
+      sum += 1e-20f;
+      uint32_t bit = 0;
+      if (lane < kTopK) {
+        const int idx = selidx[lane];
+        a.topk_idx[t * kTopK + lane] = idx;
+        a.topk_w[t * kTopK + lane] = (sv / sum) * a.routed_scaling_factor;
+        const int le = idx - a.local_expert_offset;
+        if (le >= 0 && le < kELocal) bit = 1u << le;
+      }
+      bit = __reduce_or_sync(0xFFFFFFFFu, bit);
+      if (lane == 0) a.local_mask[t] = bit;
+    }
+    // the next token's keys / gscore are written before, selidx / sels after the next first barrier;
+    // warp 0 has read selidx / sels before it reaches that barrier
+  }
+}
+
 __global__ void __launch_bounds__(1024) permute_kernel(PermuteArgs a) {
   griddep_launch_dependents();
   griddep_wait();
@@ -249,8 +321,7 @@ void launch_route_permute(const RouteArgs& r, const PermuteArgs& p, cudaStream_t
   if (r.T <= 32) {
     launch_pdl(route_permute_kernel, dim3(1), dim3(1024), 0, stream, r, p);
   } else {
-    const int grid = (r.T + 7) / 8 < 4 * kNumSMs ? (r.T + 7) / 8 : 4 * kNumSMs;
-    launch_pdl(route_kernel, dim3(grid), dim3(256), 0, stream, r);
+    launch_route_only(r, stream);
     launch_pdl(permute_kernel, dim3(1), dim3(1024), 0, stream, p);
     if (r.T > kPermuteFillInline) {
       const int chunks = (r.T + 31) / 32;
@@ -260,8 +331,12 @@ void launch_route_permute(const RouteArgs& r, const PermuteArgs& p, cudaStream_t
 }
 
 void launch_route_only(const RouteArgs& r, cudaStream_t stream) {
-  const int grid = (r.T + 7) / 8 < 4 * kNumSMs ? (r.T + 7) / 8 : 4 * kNumSMs;
-  launch_pdl(route_kernel, dim3(grid), dim3(256), 0, stream, r);
+  if (r.T <= 8 * kNumSMs) {          // one CTA per token while that is at most one wave of eight CTAs per SM
+    launch_pdl(route_block_kernel, dim3(r.T), dim3(256), 0, stream, r);
+  } else {
+    const int grid = (r.T + 7) / 8 < 4 * kNumSMs ? (r.T + 7) / 8 : 4 * kNumSMs;
+    launch_pdl(route_kernel, dim3(grid), dim3(256), 0, stream, r);
+  }
 }
 
 void launch_gather_rows(const GatherArgs& a, int T, cudaStream_t stream) {
