@@ -25,14 +25,32 @@ __device__ __forceinline__ void swiglu_split_blocks(const float* g1, size_t slab
   float4 x1[NB], x2[NB];
 #pragma unroll
   for (int b = 0; b < NB; ++b) x1[b] = x2[b] = make_float4(0.f, 0.f, 0.f, 0.f);
-  for (int s = 0; s < split; ++s) {
+  // four slabs' loads in flight at a time; the sum keeps the slab order
+  constexpr int kAhead = 4;
+  for (int s0 = 0; s0 < split; s0 += kAhead) {
+    float4 u[kAhead][NB], v[kAhead][NB];
 #pragma unroll
-    for (int b = 0; b < NB; ++b) {
-      const float* p = g1 + s * slab + static_cast<size_t>(row) * k2I + (kb0 + b) * kBlock + lane * 4;
-      const float4 u = __ldcg(reinterpret_cast<const float4*>(p));
-      const float4 v = __ldcg(reinterpret_cast<const float4*>(p + kI));
-      x1[b].x += u.x; x1[b].y += u.y; x1[b].z += u.z; x1[b].w += u.w;
-      x2[b].x += v.x; x2[b].y += v.y; x2[b].z += v.z; x2[b].w += v.w;
+    for (int d = 0; d < kAhead; ++d) {
+#pragma unroll
+      for (int b = 0; b < NB; ++b) {
+        if (s0 + d < split) {
+          const float* p = g1 + (s0 + d) * slab + static_cast<size_t>(row) * k2I + (kb0 + b) * kBlock + lane * 4;
+          u[d][b] = __ldcg(reinterpret_cast<const float4*>(p));
+          v[d][b] = __ldcg(reinterpret_cast<const float4*>(p + kI));
+        } else {
+          u[d][b] = v[d][b] = make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+      }
+    }
+#pragma unroll
+    for (int d = 0; d < kAhead; ++d) {
+      if (s0 + d < split) {
+#pragma unroll
+        for (int b = 0; b < NB; ++b) {
+          x1[b].x += u[d][b].x; x1[b].y += u[d][b].y; x1[b].z += u[d][b].z; x1[b].w += u[d][b].w;
+          x2[b].x += v[d][b].x; x2[b].y += v[d][b].y; x2[b].z += v[d][b].z; x2[b].w += v[d][b].w;
+        }
+      }
     }
   }
 #pragma unroll
@@ -46,13 +64,15 @@ __device__ __forceinline__ void swiglu_split_blocks(const float* g1, size_t slab
     float amax = fmaxf(fmaxf(fabsf(c[0]), fabsf(c[1])), fmaxf(fabsf(c[2]), fabsf(c[3])));
 #pragma unroll
     for (int d = 16; d > 0; d >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, d));
-    // power-of-two scale with amax / scale in (224, 448]
+    // power-of-two scale 2^e with amax / scale in (224, 448]: e = floor(log2(amax / 448)) + 1, clamped to
+    // [-100, 100]; read from the exponent field (a denormal quotient clamps to -100 either way)
     int e = 0;
     if (amax > 0.0f && amax < 3.0e38f) {
-      e = ilogbf(amax * (1.0f / 448.0f)) + 1;
+      e = static_cast<int>((__float_as_uint(amax * (1.0f / 448.0f)) >> 23) & 0xFFu) - 127 + 1;
       e = max(-100, min(100, e));
     }
-    const float scale = scalbnf(1.0f, e), inv = scalbnf(1.0f, -e);
+    const float scale = __uint_as_float(static_cast<uint32_t>(e + 127) << 23);
+    const float inv = __uint_as_float(static_cast<uint32_t>(127 - e) << 23);
     uint32_t packed[kNTerms];
 #pragma unroll
     for (int t = 0; t < kNTerms; ++t) packed[t] = 0;

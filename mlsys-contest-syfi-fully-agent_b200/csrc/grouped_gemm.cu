@@ -35,9 +35,7 @@
 // Every mbarrier wait is bounded (ptx.cuh); on a timeout the CTA records an error
 // bit in the schedule block and leaves through the normal teardown.
 #include "epilogue_device.cuh"
-#include "kernels.h"
-#include "ptx.cuh"
-#include "route_device.cuh"
+#include "gemm_common.cuh"
 
 namespace moe {
 
@@ -51,19 +49,7 @@ __device__ unsigned long long g_moe_trace[2][4][256];
 
 namespace {
 
-// Three warpgroups: warpgroup 0 holds the TMA producer (warp 0) and the UMMA issuer (warp 1) and gives
-// most of its registers away (setmaxnreg); warpgroups 1 and 2 are the eight promotion / epilogue warps
-// (warp % 4 = the TMEM lane quarter a warp may access) and take them.
-constexpr int kEpiWarps = 8;
-constexpr int kFirstEpiWarp = 4;
-constexpr int kThreads = (kFirstEpiWarp + kEpiWarps) * 32;
-constexpr int kRegsControl = 96;     // per thread in warpgroup 0 after the role split
-constexpr int kRegsEpilogue = 200;   // per thread in warpgroups 1 and 2
-// setmaxnreg.inc waits (unboundedly) for registers released by setmaxnreg.dec: the new total must fit
-// in what the launch allocated, 168 registers (the launch-bounds cap for 384 threads) per thread.
-constexpr int kRegsAtLaunch = 168;
-static_assert(128 * kRegsControl + 256 * kRegsEpilogue <= kRegsAtLaunch * kThreads, "register reallocation would never complete");
-static_assert(kRegsControl % 8 == 0 && kRegsEpilogue % 8 == 0, "setmaxnreg takes multiples of 8");
+constexpr int kThreads = kGemmThreads;
 
 template <int GEMM, int N_TILE>
 struct Cfg {
@@ -112,60 +98,6 @@ struct Cfg {
   static_assert(SMEM_BYTES > 116 * 1024, "one CTA per SM is assumed (TMEM is allocated without contention)");
 };
 
-struct Aux {
-  uint64_t full[10];       // TMA -> issuer: the stage's operands have landed
-  uint64_t done[10];       // issuer -> producer and promotion warps: the stage's UMMAs have completed
-  uint64_t tempty[4];      // promotion warps -> issuer: the TMEM buffer has been read
-  uint64_t esync;          // bounded replacement for a named barrier among the epilogue threads
-  uint32_t tmem_base;
-  int abort;
-  int prefix[kELocal + 1];
-  int offs[kELocal + 1];
-};
-static_assert(sizeof(Aux) <= 1024, "Aux must fit its slot");
-
-// Extra shared state of the decode-fused kernels: every CTA routes all (<= 16) tokens itself.
-struct FusedAux {
-  uint32_t keys[kEGlobal];            // order-preserving keys of the biased scores of the token being routed
-  float sval[kEGlobal];               // its unbiased sigmoid scores
-  float gscore[kNGroup];
-  int selidx[kTopK];
-  float sels[kTopK];
-  int tidx[kFusedMaxTokens][kTopK];
-  float tw[kFusedMaxTokens][kTopK];
-  uint32_t mask[kFusedMaxTokens];     // per token: selected local experts
-  uint32_t colmask[kELocal];          // per local expert: tokens that selected it
-  int items, split, n_sel_pad, n_sel;
-};
-static_assert(sizeof(FusedAux) <= 4096, "FusedAux must fit its slot");
-
-// Grid-wide barrier for a grid whose CTAs are all resident (one per SM).  The 64-bit word holds
-// {arrivals, call tag}.  CTA 0 installs {0, tag} when the kernel starts (after the wait on earlier
-// kernels, long before anybody arrives); an arriving CTA first checks that the tag is the current
-// call's, then adds one, then waits for `n` arrivals.  So the word needs no initialisation by the
-// caller and no reset between calls, and an arrival is one atomic add.  Bounded like every other
-// wait here: false on timeout.
-__device__ __forceinline__ void grid_barrier_init(unsigned int* word2, unsigned int tag) {
-  atomicExch(reinterpret_cast<unsigned long long*>(word2), static_cast<unsigned long long>(tag) << 32);
-}
-
-__device__ __forceinline__ bool grid_barrier(unsigned int* word2, unsigned int tag, unsigned int n) {
-  unsigned long long* word = reinterpret_cast<unsigned long long*>(word2);
-  __threadfence();
-  const uint64_t t0 = globaltimer_ns();
-  unsigned int spins = 0;
-  while (static_cast<unsigned int>(*reinterpret_cast<volatile unsigned long long*>(word) >> 32) != tag)
-    if ((++spins & 0xFFu) == 0 && globaltimer_ns() - t0 > MOE_WAIT_LIMIT_NS) return false;
-  atomicAdd(word, 1ull);
-  while (true) {
-    const unsigned long long v = *reinterpret_cast<volatile unsigned long long*>(word);
-    if (static_cast<unsigned int>(v) >= n) break;
-    if ((++spins & 0xFFu) == 0 && globaltimer_ns() - t0 > MOE_WAIT_LIMIT_NS) return false;
-  }
-  __threadfence();
-  return true;
-}
-
 struct Item {
   int e, m, s, row0, valid, kb0, kb1;
 };
@@ -196,19 +128,6 @@ __device__ __forceinline__ Item decode_item(int i, int split, const Aux* aux) {
   it.kb0 = ((it.s * kUnits) / split) * C::KPS;
   it.kb1 = (((it.s + 1) * kUnits) / split) * C::KPS;
   return it;
-}
-
-// CPW fp32 columns of this warp's 32 TMEM lanes -> registers.
-template <int CPW>
-__device__ __forceinline__ void tmem_ld_cols(uint32_t taddr, float* v) {
-  if constexpr (CPW == 8) {
-    tmem_ld8(taddr, v);
-  } else if constexpr (CPW == 16) {
-    tmem_ld16(taddr, v);
-  } else {
-#pragma unroll
-    for (int c = 0; c < CPW / 32; ++c) tmem_ld32(taddr + c * 32, v + c * 32);
-  }
 }
 
 template <int GEMM, int N_TILE, bool FUSED = false>
@@ -248,186 +167,9 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
   int items, split, n_sel_pad;
   FusedAux* fa = reinterpret_cast<FusedAux*>(reinterpret_cast<uint8_t*>(aux) + 1024);
   if constexpr (FUSED && GEMM == 1) {
-    // Decode path: no routing / permutation / gather kernels ran.  Every CTA routes all tokens and
-    // derives the same schedule in shared memory; CTA 0 also publishes it for the later kernel.
     static_assert(N_TILE == kFusedMaxTokens, "the fused path puts every token in one token tile");
-    if (a.T <= 2) {
-      // Block-cooperative routing (same arithmetic and tie rules as route_token): thread e < 256 owns
-      // expert e, so warp g is routing group g.  Per token: sigmoid + bias, the group's two best by
-      // two warp reductions, then every kept expert counts how many kept experts beat it; the eight
-      // with rank < 8 are the selection in descending order.  ~1k cycles per token instead of the
-      // ~7k of one warp doing eight rounds of arg-max.
-      const int e = threadIdx.x;
-      float* xs = reinterpret_cast<float*>(smem);                 // [T][256] logits; the stage ring is still idle
-      float bias_e = 0.0f;
-      if (e < kEGlobal) {
-        bias_e = __uint_as_float(static_cast<uint32_t>(a.bias_bf16[e]) << 16);
-        for (int t = 0; t < a.T; ++t) xs[t * kEGlobal + e] = a.logits[static_cast<size_t>(t) * kEGlobal + e];
-      }
-      if (threadIdx.x == 0) TRACE(3, 6);
-      for (int t = 0; t < a.T; ++t) {
-        float s_e = 0.0f;
-        uint32_t key_e = 0;
-        if (e < kEGlobal) {
-          s_e = 1.0f / (1.0f + expf(-xs[t * kEGlobal + e]));
-          key_e = order_key(s_e + bias_e);
-          fa->keys[e] = key_e;
-          fa->sval[e] = s_e;
-          const uint32_t k1 = __reduce_max_sync(0xFFFFFFFFu, key_e);
-          const int first = __ffs(__ballot_sync(0xFFFFFFFFu, key_e == k1)) - 1;
-          const uint32_t k2 = __reduce_max_sync(0xFFFFFFFFu, lane == first ? 0u : key_e);
-          const uint32_t u1 = (k1 & 0x80000000u) ? (k1 & 0x7FFFFFFFu) : ~k1;
-          const uint32_t u2 = (k2 & 0x80000000u) ? (k2 & 0x7FFFFFFFu) : ~k2;
-          if (lane == 0) fa->gscore[warp] = __uint_as_float(u1) + __uint_as_float(u2);
-        }
-        __syncthreads();
-        if (e < kEGlobal) {
-          uint32_t keep = 0;
-  #pragma unroll
-          for (int g = 0; g < kNGroup; ++g) {
-            int rank = 0;
-  #pragma unroll
-            for (int h2 = 0; h2 < kNGroup; ++h2)
-              rank += (fa->gscore[h2] > fa->gscore[g]) || (fa->gscore[h2] == fa->gscore[g] && h2 < g);
-            keep |= (rank < kTopKGroup ? 1u : 0u) << g;
-          }
-          if ((keep >> warp) & 1u) {
-            int rank = 0;
-            for (int g = 0; g < kNGroup; ++g) {
-              if (!((keep >> g) & 1u)) continue;
-              const uint4* kv = reinterpret_cast<const uint4*>(fa->keys + g * 32);
-  #pragma unroll
-              for (int c = 0; c < 8; ++c) {
-                const uint4 k = kv[c];
-                const int j = g * 32 + c * 4;
-                rank += (k.x > key_e) || (k.x == key_e && j + 0 < e);
-                rank += (k.y > key_e) || (k.y == key_e && j + 1 < e);
-                rank += (k.z > key_e) || (k.z == key_e && j + 2 < e);
-                rank += (k.w > key_e) || (k.w == key_e && j + 3 < e);
-              }
-            }
-            if (rank < kTopK) { fa->selidx[rank] = e; fa->sels[rank] = s_e; }
-          }
-        }
-        __syncthreads();
-        if (warp == 0) {
-          const float sv = lane < kTopK ? fa->sels[lane] : 0.0f;
-          float sum = 0.0f;
-  #pragma unroll
-          for (int k = 0; k < kTopK; ++k) sum += __shfl_sync(0xFFFFFFFFu, sv, k);
-          sum += 1e-20f;
-          uint32_t bit = 0;
-          if (lane < kTopK) {
-            const int idx = fa->selidx[lane];
-            fa->tidx[t][lane] = idx;
-            fa->tw[t][lane] = (sv / sum) * a.routed_scaling_factor;
-            const int le = idx - a.local_expert_offset;
-            if (le >= 0 && le < kELocal) bit = 1u << le;
-          }
-          bit = __reduce_or_sync(0xFFFFFFFFu, bit);
-          if (lane == 0) fa->mask[t] = bit;
-        }
-      }
-    } else {
-      // More than two tokens: one warp per token (ten at a time), each doing the warp-level routing.
-      float* bias_s = fa->sval;                                  // 256 floats, free on this path
-      for (int i = threadIdx.x; i < kEGlobal; i += kThreads)
-        bias_s[i] = __uint_as_float(static_cast<uint32_t>(a.bias_bf16[i]) << 16);
-      __syncthreads();
-      for (int t = warp; t < a.T; t += kThreads / 32) {
-        int idx;
-        float w;
-        route_token(a.logits + static_cast<size_t>(t) * kEGlobal, bias_s, a.routed_scaling_factor, lane, idx, w);
-        uint32_t bit = 0;
-        if (lane < kTopK) {
-          fa->tidx[t][lane] = idx;
-          fa->tw[t][lane] = w;
-          const int le = idx - a.local_expert_offset;
-          if (le >= 0 && le < kELocal) bit = 1u << le;
-        }
-        bit = __reduce_or_sync(0xFFFFFFFFu, bit);
-        if (lane == 0) fa->mask[t] = bit;
-      }
-    }
-    if (threadIdx.x == 0) TRACE(3, 7);
-    fence_proxy_async_smem();   // the logits scratch is about to be overwritten by TMA (async proxy)
-    __syncthreads();
-    if (threadIdx.x == 0) TRACE(3, 8);
-    if (warp == 0) {                     // lane = local expert
-      uint32_t cm = 0;
-      for (int t = 0; t < a.T; ++t) cm |= ((fa->mask[t] >> lane) & 1u) << t;
-      const int c = __popc(cm);
-      int inc = c, tinc = c > 0 ? 1 : 0;
-#pragma unroll
-      for (int d = 1; d < 32; d <<= 1) {
-        const int v = __shfl_up_sync(0xFFFFFFFFu, inc, d);
-        const int tv = __shfl_up_sync(0xFFFFFFFFu, tinc, d);
-        if (lane >= d) { inc += v; tinc += tv; }
-      }
-      fa->colmask[lane] = cm;
-      aux->offs[lane + 1] = inc;
-      aux->prefix[lane + 1] = tinc;
-      const uint32_t act = __ballot_sync(0xFFFFFFFFu, c > 0);
-      const int n_sel = __shfl_sync(0xFFFFFFFFu, inc, 31), tiles_total = __shfl_sync(0xFFFFFFFFu, tinc, 31);
-      const int pad = (n_sel + 15) & ~15;
-      const int s1 = choose_split_warp(tiles_total * kMT1, kMaxSplit1, a.ctas, pad, a.slab_rows, lane, kKB1,
-                                       Cfg<1, kFusedMaxTokens>::KPS);
-      const int s2 = choose_split_warp(tiles_total * kMT2, kMaxSplit2, a.ctas, pad, a.slab_rows, lane, kKB2,
-                                       Cfg<2, kFusedMaxTokens>::KPS);
-      if (lane == 0) {
-        aux->offs[0] = 0;
-        aux->prefix[0] = 0;
-        fa->items = tiles_total * kMT1 * s1;
-        fa->split = s1;
-        fa->n_sel_pad = pad;
-        fa->n_sel = n_sel;
-      }
-      if (blockIdx.x == 0) {
-        sched->counts[lane] = c;
-        sched->offs[lane + 1] = inc;
-        sched->tile_prefix[lane + 1] = tinc;
-        sched->tile_prefix2[lane + 1] = tinc;
-        if (lane == 0) {
-          sched->offs[0] = 0;
-          sched->tile_prefix[0] = 0;
-          sched->tile_prefix2[0] = 0;
-          sched->n_tile2 = N_TILE;
-          sched->status = 0;
-          sched->n_sel = n_sel;
-          sched->n_sel_pad = pad;
-          sched->n_active = __popc(act);
-          sched->n_tile = N_TILE;
-          sched->tiles_total = tiles_total;
-          sched->split1 = s1;
-          sched->split2 = s2;
-          sched->items1 = tiles_total * kMT1 * s1;
-          sched->items2 = tiles_total * kMT2 * s2;
-        }
-      }
-    }
-    __syncthreads();
-    if (blockIdx.x == 0 && warp == kFirstEpiWarp && lane < a.T) {   // lane = token: selection, permutation, row lists
-      const int t = lane;
-      const uint32_t m = fa->mask[t];
-      a.local_mask[t] = m;
-#pragma unroll
-      for (int k = 0; k < kTopK; ++k) {
-        a.topk_idx[t * kTopK + k] = fa->tidx[t][k];
-        a.topk_w[t * kTopK + k] = fa->tw[t][k];
-      }
-      int j = 0;
-      for (uint32_t rest = m; rest; rest &= rest - 1, ++j) {
-        const int le = __ffs(rest) - 1;
-        const int row = aux->offs[le] + __popc(fa->colmask[le] & ((1u << t) - 1u));
-        float w = 0.0f;
-#pragma unroll
-        for (int k = 0; k < kTopK; ++k)
-          if (fa->tidx[t][k] - a.local_expert_offset == le) w = fa->tw[t][k];
-        a.perm_token[row] = t;
-        a.perm_weight[row] = w;
-        a.tok_rows[t * kTopK + j] = row;
-      }
-    }
+    static_assert(Cfg<1, N_TILE>::KPS == kDecodeKps && Cfg<2, N_TILE>::KPS == kDecodeKps, "split-K granularity");
+    decode_route_schedule(a, smem, aux, fa, sched);
     items = fa->items;
     split = fa->split;
     n_sel_pad = fa->n_sel_pad;

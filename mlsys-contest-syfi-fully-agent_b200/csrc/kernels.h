@@ -126,6 +126,11 @@ int launch_grouped_gemm(int gemm_id, int n_tile, const CUtensorMap& tm_w, const 
 int launch_fused_gemm(int gemm_id, const CUtensorMap& tm_w, const CUtensorMap& tm_b, const GemmArgs& a, int ctas,
                       cudaStream_t stream);
 constexpr int kFusedMaxTokens = 16;
+// Decode path in one launch: routing, GEMM1, SwiGLU, GEMM2 and combine (decode_kernel.cu).  `g` is the GEMM1 view
+// of the arguments with all routing / tail fields set; tm_x maps hidden_states, tm_c the SwiGLU planes.
+int launch_decode(const CUtensorMap& tm_w1, const CUtensorMap& tm_x, const CUtensorMap& tm_w2, const CUtensorMap& tm_c,
+                  const GemmArgs& g, const float* w2_scale, float* o, int ctas, cudaStream_t stream);
+int decode_kernel_init();
 int grouped_gemm_kblocks_per_stage(int gemm_id, int n_tile);   // K-blocks one TMA box of that kernel brings
 int grouped_gemm_init();   // one-time function attributes (dynamic shared memory opt-in)
 void launch_swiglu_split(const SwigluArgs& a, int T, cudaStream_t stream);

@@ -123,6 +123,7 @@ int ensure_device(DeviceState** out) {
     if (fn == nullptr || qres != cudaDriverEntryPointSuccess) return MOE_B200_EDEVICE;
     d.encode = reinterpret_cast<EncodeFn>(fn);
     int rc = grouped_gemm_init();
+    if (rc == 0) rc = decode_kernel_init();
     if (rc != 0) {
       g_last_cuda_error = rc;
       return MOE_B200_ECUDA;
@@ -197,12 +198,14 @@ int pick_n_tile(int T) {
   return T <= 16 ? 16 : T <= 32 ? 32 : T <= 64 ? 64 : 128;
 }
 
-bool use_fused_decode() {
-  static const bool on = [] {
+// Decode path selection (MOE_B200_FUSED_DECODE): 1 = one launch (default), 2 = two launches (a fused
+// kernel per GEMM), 0 = the general seven-kernel path.
+int fused_decode_mode() {
+  static const int mode = [] {
     const char* s = std::getenv("MOE_B200_FUSED_DECODE");
-    return !(s && s[0] == '0');
+    return s ? std::atoi(s) : 1;
   }();
-  return on;
+  return mode;
 }
 
 bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
@@ -294,7 +297,7 @@ static int run_impl(const float* routing_logits, const uint16_t* routing_bias, c
   if ((rc = get_map(dev, kblock_map(a_packed, L.rows_cap, kH, n_tile, kps1), &tm_a))) return rc;
   if ((rc = get_map(dev, planes_map(cq, L.rows_cap, n_tile2, kps2), &tm_c))) return rc;
 
-  if (T <= kFusedMaxTokens && use_fused_decode()) {
+  if (T <= kFusedMaxTokens && fused_decode_mode() != 0) {
     // Decode path: two launches.  GEMM1 routes in-kernel, reads the token rows straight from
     // hidden_states (all tokens are one token tile) and ends with SwiGLU; GEMM2 ends with the combine.
     static std::atomic<unsigned int> call_counter{0x9E3779B1u};
@@ -310,6 +313,16 @@ static int run_impl(const float* routing_logits, const uint16_t* routing_bias, c
     fa.topk_idx = topk_idx; fa.topk_w = topk_w; fa.local_mask = local_mask;
     fa.perm_token = perm_token; fa.perm_weight = perm_weight; fa.tok_rows = tok_rows;
     fa.cq = cq; fa.c_scale = c_scale; fa.out_bf16 = output; fa.out_rows = output_rows;
+    if (fused_decode_mode() == 1) {
+      stage_mark(0, stream); stage_mark(1, stream); stage_mark(2, stream);
+      if ((rc = launch_decode(tm_w13, tm_h, tm_w2, tm_c, fa, gemm2_weights_scale, o, ctas, stream))) {
+        g_last_cuda_error = rc;
+        return MOE_B200_ECUDA;
+      }
+      stage_mark(3, stream); stage_mark(4, stream); stage_mark(5, stream); stage_mark(6, stream);
+      g_launches += 1;
+      return MOE_B200_OK;
+    }
     stage_mark(0, stream); stage_mark(1, stream); stage_mark(2, stream);
     if ((rc = launch_fused_gemm(1, tm_w13, tm_h, fa, ctas, stream))) { g_last_cuda_error = rc; return MOE_B200_ECUDA; }
     stage_mark(3, stream); stage_mark(4, stream);

@@ -21,9 +21,9 @@ DEFINITION = "moe_fp8_block_scale_ds_routing_topk8_ng8_kg4_e32_h7168_i2048"
 AUTHOR = "b200-native"
 ENTRY_POINT = "tvm_ffi_shim.cu::run"
 
-SOURCE_FILES = ["tvm_ffi_shim.cu", "launcher.cu", "route_permute.cu", "grouped_gemm.cu", "swiglu_combine.cu",
+SOURCE_FILES = ["tvm_ffi_shim.cu", "launcher.cu", "route_permute.cu", "grouped_gemm.cu", "decode_kernel.cu", "swiglu_combine.cu",
                 "static_entry.cu", "quantize.cu", "ep_push.cu", "kernels.h", "moe_layout.h", "ptx.cuh", "route_device.cuh",
-                "epilogue_device.cuh"]
+                "epilogue_device.cuh", "gemm_common.cuh"]
 
 
 def flattened_sources():
