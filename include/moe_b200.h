@@ -146,7 +146,7 @@ typedef struct moe_b200_layout {
 typedef struct moe_b200_sched {
   int32_t status, n_sel, n_sel_pad, n_active, n_tile, tiles_total, split1, split2, items1, items2;
   uint32_t bar1[2], bar2[2];
-  int32_t n_tile2, pad_[1];
+  int32_t n_tile2, ctas;
   int32_t counts[32];
   int32_t offs[33];
   int32_t tile_prefix[33];

@@ -17,6 +17,13 @@
 //   warp 0      TMA producer (one thread)          warps 4-11  promotion + epilogue + tails
 //   warp 1      UMMA issuer  (one thread)          (same roles and ring protocol as grouped_gemm.cu)
 //
+// Work split ("stream-K"): a GEMM's work is the sequence of pipeline stages (2 K-blocks) of all its
+// (expert, weight-row tile) pairs, tile-major; CTA c takes the stages [c*G/n, (c+1)*G/n), i.e. a contiguous
+// run that may cover the end of one tile and the start of the next.  Every CTA streams the same number of
+// bytes (+-1 stage) whatever the number of active experts.  The pieces of a tile go to separate fp32 slabs
+// (slab = ordinal of the piece in its tile, computable from the tile index alone), which the next phase
+// sums in order: deterministic.
+//
 // Phases of a CTA:  setup | routing + schedule (every CTA, identical result) | GEMM1 items -> fp32
 // split-K slabs | grid barrier 1 | SwiGLU + 3-plane e4m3 split of this CTA's share of (row, K-block)
 // units | grid barrier 2 | GEMM2 items -> fp32 slabs | grid barrier 3 | weighted combine -> bf16.
@@ -26,7 +33,7 @@
 #include "ptx.cuh"
 #ifdef MOE_TRACE
 // Debug build only: time stamps (ns) of every CTA, [cta][role][slot].
-namespace moe { __device__ unsigned long long g_moe_dtrace[148][4][8]; }
+namespace moe { __device__ unsigned long long g_moe_dtrace[148][4][16]; }
 #define DTRACE(role, slot) do { if (blockIdx.x < 148) moe::g_moe_dtrace[blockIdx.x][role][slot] = moe::globaltimer_ns(); } while (0)
 #define MOE_ROUTE_TRACE(slot) DTRACE(3, slot)
 #else
@@ -70,27 +77,47 @@ struct DItem {
   int e, m, s, row0, valid, kb0, kb1;
 };
 
-template <int GEMM>
-__device__ __forceinline__ DItem ditem(int i, int split, const Aux* aux) {
-  constexpr int MT = GEMM == 1 ? kMT1 : kMT2;
-  constexpr int KB = GEMM == 1 ? kKB1 : kKB2;
-  const int per = MT * split;
-  int e = 0;   // largest e with prefix[e] * per <= i (an expert has one token tile or none)
-#pragma unroll 1
-  for (int k = 16; k > 0; k >>= 1)
-    if (e + k < kELocal && aux->prefix[e + k] * per <= i) e += k;
-  const int r = i - aux->prefix[e] * per;
-  DItem it;
-  it.e = e;
-  it.s = r % split;
-  it.m = r / split;
-  it.row0 = aux->offs[e];
-  it.valid = aux->offs[e + 1] - aux->offs[e];
-  constexpr int kUnits = KB / DC::KPS;
-  it.kb0 = ((it.s * kUnits) / split) * DC::KPS;
-  it.kb1 = (((it.s + 1) * kUnits) / split) * DC::KPS;
-  return it;
+// CTA that owns stage g of a sequence of G stages cut into n contiguous runs [c*G/n, (c+1)*G/n).
+__device__ __forceinline__ int stage_owner(int g, int G, int n) { return ((g + 1) * n - 1) / G; }
+
+// Number of pieces (= slabs) of tile `tau` whose stages are [tau*U, tau*U + U).
+__device__ __forceinline__ int tile_pieces(int tau, int U, int G, int n) {
+  return stage_owner(tau * U + U - 1, G, n) - stage_owner(tau * U, G, n) + 1;
 }
+
+// This CTA's share of one GEMM, delivered piece by piece.
+template <int GEMM>
+struct Part {
+  static constexpr int MT = GEMM == 1 ? kMT1 : kMT2;
+  static constexpr int U = (GEMM == 1 ? kKB1 : kKB2) / DC::KPS;   // stages per tile
+  int g, g1, G, cta, n;
+  __device__ __forceinline__ void init(int tiles, int cta_, int n_) {
+    G = tiles * MT * U;
+    cta = cta_;
+    n = n_;
+    g = cta * G / n;
+    g1 = (cta + 1) * G / n;
+  }
+  __device__ __forceinline__ bool next(const Aux* aux, DItem& it) {
+    if (g >= g1) return false;
+    const int tau = g / U, u0 = g - tau * U;
+    const int len = min(U - u0, g1 - g);
+    const int ord = tau / MT;   // ordinal of the expert among the active ones
+    int e = 0;                  // largest e with prefix[e] <= ord: the ord-th active expert
+#pragma unroll 1
+    for (int k = 16; k > 0; k >>= 1)
+      if (e + k < kELocal && aux->prefix[e + k] <= ord) e += k;
+    it.e = e;
+    it.m = tau - ord * MT;
+    it.s = cta - stage_owner(tau * U, G, n);
+    it.row0 = aux->offs[e];
+    it.valid = aux->offs[e + 1] - aux->offs[e];
+    it.kb0 = u0 * DC::KPS;
+    it.kb1 = (u0 + len) * DC::KPS;
+    g += len;
+    return true;
+  }
+};
 
 __device__ __forceinline__ void fence_proxy_async_global() { asm volatile("fence.proxy.async.global;" ::: "memory"); }
 
@@ -105,23 +132,30 @@ struct Ring {
 
 // UMMA issue of one GEMM's items (one thread).
 template <int GEMM>
-__device__ __forceinline__ bool issue_items(int items, int split, const Aux* aux, uint32_t smem_base, uint32_t tmem_base,
-                                            Ring& r, volatile int* abort_flag) {
+__device__ __forceinline__ bool issue_items(int tiles, const Aux* aux, uint32_t smem_base, uint32_t tmem_base, Ring& r,
+                                            volatile int* abort_flag) {
   constexpr int BB = GEMM == 1 ? DC::B1_BYTES : DC::B2_BYTES;
   constexpr int COLS = GEMM == 1 ? DC::COLS1 : DC::COLS2;
   constexpr uint32_t idesc = umma_idesc_e4m3(128, COLS);
   const uint64_t desc_const = umma_desc_k_sw128(0);
   const uint32_t full_base = smem_u32(&aux->full[0]), done_base = smem_u32(&aux->done[0]);
   const uint32_t tempty_base = smem_u32(&aux->tempty[0]);
-  for (int i = blockIdx.x; i < items; i += gridDim.x) {
-    const DItem w = ditem<GEMM>(i, split, aux);
+  Part<GEMM> part;
+  part.init(tiles, blockIdx.x, gridDim.x);
+  DItem w;
+  bool first = true;
+  for (; part.next(aux, w); first = false) {
     for (int kb = w.kb0; kb < w.kb1; kb += DC::KPS) {
       if (!mbar_wait(tempty_base + r.buf * 8, r.bph ^ 1u, abort_flag)) return false;
       if (!mbar_wait(full_base + r.stage * 8, r.ph, abort_flag)) return false;
 #ifdef MOE_TRACE
-      if (GEMM == 2 && i == static_cast<int>(blockIdx.x) && kb < w.kb0 + 4 * DC::KPS) DTRACE(0, 4 + (kb - w.kb0) / DC::KPS);
+      if (GEMM == 2 && first && kb < w.kb0 + 4 * DC::KPS) DTRACE(0, 4 + (kb - w.kb0) / DC::KPS);
 #endif
       tc_fence_after_sync();
+#ifdef MOE_TRACE
+      const bool tr = GEMM == 2 && first && kb == w.kb0 + 2 * DC::KPS;
+      if (tr) moe::g_moe_dtrace[blockIdx.x][3][8] = clock64();
+#endif
       const uint32_t sbase = smem_base + r.stage * DC::STAGE_BYTES;
 #pragma unroll
       for (int u = 0; u < DC::KPS; ++u) {
@@ -131,9 +165,15 @@ __device__ __forceinline__ bool issue_items(int items, int split, const Aux* aux
 #pragma unroll
         for (int k4 = 0; k4 < 4; ++k4) umma_f8(d, adesc + 2 * k4, bdesc + 2 * k4, idesc, k4 != 0 ? 1u : 0u);
       }
+#ifdef MOE_TRACE
+      if (tr) moe::g_moe_dtrace[blockIdx.x][3][9] = clock64();
+#endif
       umma_commit(done_base + r.stage * 8);
-      if (GEMM == 2 && i == static_cast<int>(blockIdx.x) && kb == w.kb0) DTRACE(1, 4);
-      if (GEMM == 2 && i == static_cast<int>(blockIdx.x) && kb == w.kb0 + 3 * DC::KPS) DTRACE(1, 5);
+#ifdef MOE_TRACE
+      if (tr) moe::g_moe_dtrace[blockIdx.x][3][10] = clock64();
+#endif
+      if (GEMM == 2 && first && kb == w.kb0) DTRACE(1, 4);
+      if (GEMM == 2 && first && kb == w.kb0 + 3 * DC::KPS) DTRACE(1, 5);
       if (GEMM == 2) DTRACE(1, 6);
       r.advance();
     }
@@ -181,10 +221,9 @@ __device__ __forceinline__ float scale_product(const DecodeArgs& a, const FusedA
   }
 }
 
-// Promotion + store of one GEMM's items by the eight promotion warps.
+// Promotion + store of this CTA's pieces of one GEMM by the eight promotion warps.
 template <int GEMM>
-__device__ __forceinline__ void promote_items(const DecodeArgs& a, EpiCtx& c, int items, int split, int n_sel_pad,
-                                              float ws2_first) {
+__device__ __forceinline__ void promote_items(const DecodeArgs& a, EpiCtx& c, int tiles, int n_sel_pad, float ws2_first) {
   constexpr int KB = GEMM == 1 ? kKB1 : kKB2;
   constexpr int M_TOTAL = GEMM == 1 ? k2I : kH;
   constexpr int COLS = GEMM == 1 ? DC::COLS1 : DC::COLS2;
@@ -198,8 +237,12 @@ __device__ __forceinline__ void promote_items(const DecodeArgs& a, EpiCtx& c, in
   float* out_base = GEMM == 1 ? a.g.out : a.o;
   float pre[kMaxE];
   uint32_t nitem = 0;
-  if (static_cast<int>(blockIdx.x) < items) {
-    const DItem w0 = ditem<GEMM>(blockIdx.x, split, c.aux);
+  Part<GEMM> part;
+  part.init(tiles, blockIdx.x, gridDim.x);
+  DItem w, wn;
+  bool have = part.next(c.aux, w);
+  if (have) {
+    const DItem& w0 = w;
 #pragma unroll
     for (int x = 0; x < kMaxE; ++x) {
       const int idx = c.etid + x * kEpiThreads;
@@ -214,16 +257,14 @@ __device__ __forceinline__ void promote_items(const DecodeArgs& a, EpiCtx& c, in
       }
     }
   }
-  for (int i = blockIdx.x; c.ok && i < items; i += gridDim.x, ++nitem) {
-    const DItem w = ditem<GEMM>(i, split, c.aux);
+  for (; c.ok && have; ++nitem) {
     const int nkb = w.kb1 - w.kb0;
     const float* sc = c.sc_base + (nitem & 1u) * DC::SC_FLOATS;
-    const int inext = i + gridDim.x;
-    c.sync();   // this item's table is complete and the other one is free
+    const bool have_next = part.next(c.aux, wn);
+    c.sync();   // this piece's table is complete and the other one is free
     if (!c.ok) break;
     if (GEMM == 2 && nitem == 0 && c.etid == 0) DTRACE(2, 6);
-    if (inext < items) {
-      const DItem wn = ditem<GEMM>(inext, split, c.aux);
+    if (have_next) {
 #pragma unroll
       for (int x = 0; x < kMaxE; ++x) pre[x] = scale_product<GEMM>(a, c.fa, wn, c.etid + x * kEpiThreads);
     }
@@ -282,7 +323,7 @@ __device__ __forceinline__ void promote_items(const DecodeArgs& a, EpiCtx& c, in
       for (int j = 0; j < CPW; ++j)
         if (c.h * CPW + j < w.valid) out[static_cast<size_t>(j) * M_TOTAL] = acc[j];
     }
-    if (inext < items) {
+    if (have_next) {
       float* scn = c.sc_base + ((nitem + 1) & 1u) * DC::SC_FLOATS;
 #pragma unroll
       for (int x = 0; x < kMaxE; ++x) {
@@ -290,6 +331,8 @@ __device__ __forceinline__ void promote_items(const DecodeArgs& a, EpiCtx& c, in
         if (idx < KB * kNT) scn[idx] = pre[x];
       }
     }
+    w = wn;
+    have = have_next;
   }
 }
 
@@ -335,7 +378,11 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_w1, const __grid_constant__
   tc_fence_before_sync();
   __syncthreads();
   tc_fence_after_sync();
-  const int items1 = fa->items, split1 = fa->split, items2 = fa->items2, split2 = fa->split2;
+  const int tiles = fa->tiles;
+  // a tile has at most n / tiles-of-the-GEMM + 2 pieces; the SwiGLU phase sums up to 8 slabs
+  if (threadIdx.x == 0 && tiles > 0 && static_cast<int>(gridDim.x) / (tiles * kMT1) + 2 > 8) {
+    atomicOr(&sched->status, kErrSchedOverflow);
+  }
   const int n_sel_pad = fa->n_sel_pad;
   const uint32_t tmem_base = aux->tmem_base;
   volatile int* abort_flag = &aux->abort;
@@ -351,33 +398,36 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_w1, const __grid_constant__
         const uint32_t full_base = smem_u32(&aux->full[0]), done_base = smem_u32(&aux->done[0]);
         uint32_t stage = 0, ph = 0;
         bool ok = true;
-        for (int i = blockIdx.x; ok && i < items1; i += gridDim.x) {
-          const DItem w = ditem<1>(i, split1, aux);
-          const int wy = w.e * k2I + w.m * 128;
-          for (int kb = w.kb0; kb < w.kb1; kb += DC::KPS) {
-            if (!mbar_wait(done_base + stage * 8, ph ^ 1u, abort_flag)) { ok = false; break; }
-            const uint32_t fb = full_base + stage * 8;
-            mbar_arrive_expect_tx(fb, DC::TX1);
-            const uint32_t dst = smem_base + stage * DC::STAGE_BYTES;
-            tma_load_3d(dst, &tm_w1, 0, wy, kb, fb);                 // [2 K-blocks][128 rows][128 B]
-            tma_load_3d(dst + DC::B_OFF, &tm_x, 0, 0, kb, fb);       // [2 K-blocks][16 tokens][128 B]
-            if (++stage == DC::STAGES) { stage = 0; ph ^= 1u; }
+        {
+          Part<1> part;
+          part.init(tiles, blockIdx.x, gridDim.x);
+          DItem w;
+          while (ok && part.next(aux, w)) {
+            const int wy = w.e * k2I + w.m * 128;
+            for (int kb = w.kb0; kb < w.kb1; kb += DC::KPS) {
+              if (!mbar_wait(done_base + stage * 8, ph ^ 1u, abort_flag)) { ok = false; break; }
+              const uint32_t fb = full_base + stage * 8;
+              mbar_arrive_expect_tx(fb, DC::TX1);
+              const uint32_t dst = smem_base + stage * DC::STAGE_BYTES;
+              tma_load_3d(dst, &tm_w1, 0, wy, kb, fb);                 // [2 K-blocks][128 rows][128 B]
+              tma_load_3d(dst + DC::B_OFF, &tm_x, 0, 0, kb, fb);       // [2 K-blocks][16 tokens][128 B]
+              if (++stage == DC::STAGES) { stage = 0; ph ^= 1u; }
+            }
           }
         }
         DTRACE(1, 0);
         // GEMM2: the weight box of a stage is requested as soon as the stage is free, up to a full ring
         // ahead of the token-operand boxes, which wait for the planes (grid barrier 2).
-        int wi = blockIdx.x, wkb = 0, bi = blockIdx.x, bkb = 0, ahead = 0;
+        Part<2> wpart, bpart;
+        wpart.init(tiles, blockIdx.x, gridDim.x);
+        bpart = wpart;
         DItem ww{}, bw{};
-        if (wi < items2) {
-          ww = ditem<2>(wi, split2, aux);
-          bw = ww;
-          wkb = bkb = ww.kb0;
-        }
+        bool whave = wpart.next(aux, ww), bhave = bpart.next(aux, bw);
+        int wkb = ww.kb0, bkb = bw.kb0, ahead = 0;
         uint32_t bstage = stage;
         bool ready = false;
-        while (ok && bi < items2) {
-          if (ready ? ahead > 0 : (ahead == DC::STAGES || wi >= items2)) {
+        while (ok && bhave) {
+          if (ready ? ahead > 0 : (ahead == DC::STAGES || !whave)) {
             if (!ready) {
               DTRACE(1, 1);
               if (!grid_barrier_wait(bar, a.g.call_tag, 2 * n_ctas)) { *abort_flag = 1; ok = false; break; }
@@ -391,8 +441,8 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_w1, const __grid_constant__
             --ahead;
             bkb += DC::KPS;
             if (bkb >= bw.kb1) {
-              bi += gridDim.x;
-              if (bi < items2) { bw = ditem<2>(bi, split2, aux); bkb = bw.kb0; }
+              bhave = bpart.next(aux, bw);
+              bkb = bw.kb0;
             }
           } else {
             if (!mbar_wait(done_base + stage * 8, ph ^ 1u, abort_flag)) { ok = false; break; }
@@ -403,8 +453,8 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_w1, const __grid_constant__
             ++ahead;
             wkb += DC::KPS;
             if (wkb >= ww.kb1) {
-              wi += gridDim.x;
-              if (wi < items2) { ww = ditem<2>(wi, split2, aux); wkb = ww.kb0; }
+              whave = wpart.next(aux, ww);
+              wkb = ww.kb0;
             }
           }
         }
@@ -416,8 +466,8 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_w1, const __grid_constant__
       if (lane == 0) {
         Ring r;
         const uint32_t smem_base = smem_u32(smem);
-        if (issue_items<1>(items1, split1, aux, smem_base, tmem_base, r, abort_flag))
-          issue_items<2>(items2, split2, aux, smem_base, tmem_base, r, abort_flag);
+        if (issue_items<1>(tiles, aux, smem_base, tmem_base, r, abort_flag))
+          issue_items<2>(tiles, aux, smem_base, tmem_base, r, abort_flag);
       }
       __syncwarp();
     }
@@ -438,14 +488,16 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_w1, const __grid_constant__
     // arrivals are only valid once CTA 0 has installed this launch's tag; checked here, long before the first one
     if (c.etid == 0 && !grid_barrier_tag_wait(bar, a.g.call_tag)) *abort_flag = 1;
 
-    promote_items<1>(a, c, items1, split1, n_sel_pad, 0.0f);
+    promote_items<1>(a, c, tiles, n_sel_pad, 0.0f);
     if (c.etid == 0) DTRACE(2, 0);
 
     // first GEMM2 item: the weight-scale factor of this thread's table entry does not depend on GEMM1;
     // fetching it here takes its DRAM latency off the path between grid barrier 2 and the first promotion
     float ws2_first = 0.0f;
-    if (static_cast<int>(blockIdx.x) < items2) {
-      const DItem w0 = ditem<2>(blockIdx.x, split2, aux);
+    Part<2> first2;
+    first2.init(tiles, blockIdx.x, gridDim.x);
+    DItem w0;
+    if (first2.next(aux, w0)) {
       const int kbl = c.etid / kNT;
       if (kbl < w0.kb1 - w0.kb0)
         // (volatile: the compiler would otherwise sink the load to its use, after both barriers)
@@ -470,10 +522,18 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_w1, const __grid_constant__
       const int fill_rows = min(n_sel + kNT - 1, a.g.rows_cap);
       const int units = fill_rows * kKB2;
       const size_t slab = static_cast<size_t>(n_sel_pad) * k2I;
+      constexpr int U1 = Part<1>::U;
+      const int G1 = tiles * kMT1 * U1;
       for (int u = blockIdx.x * kEpiWarps + (warp - kFirstEpiWarp); u < units; u += gridDim.x * kEpiWarps) {
         const int row = u / kKB2, kb = u % kKB2;
         if (row < n_sel) {
-          swiglu_split_unit(a.g.out, slab, split1, row, kb, lane, a.g.cq, a.g.c_scale, a.g.rows_cap);
+          int e = 0;   // the row's expert: largest e with offs[e] <= row
+#pragma unroll 1
+          for (int k = 16; k > 0; k >>= 1)
+            if (e + k < kELocal && aux->offs[e + k] <= row) e += k;
+          const int tau = aux->prefix[e] * kMT1 + kb;   // weight tile of x1; x2's is 16 tiles further
+          swiglu_split_unit2(a.g.out, slab, tile_pieces(tau, U1, G1, n_ctas), tile_pieces(tau + kKB2, U1, G1, n_ctas), row,
+                             kb, lane, a.g.cq, a.g.c_scale, a.g.rows_cap);
         } else {
 #pragma unroll
           for (int t = 0; t < kNTerms; ++t)
@@ -495,7 +555,7 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_w1, const __grid_constant__
     c.sync();
     if (c.etid == 0) DTRACE(2, 2);
 
-    if (c.ok && !*abort_flag) promote_items<2>(a, c, items2, split2, n_sel_pad, ws2_first);
+    if (c.ok && !*abort_flag) promote_items<2>(a, c, tiles, n_sel_pad, ws2_first);
     if (c.etid == 0) DTRACE(2, 3);
 
     // grid barrier 3: every GEMM2 slab is complete
@@ -508,11 +568,21 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_w1, const __grid_constant__
     if (c.etid == 0) DTRACE(2, 4);
     if (c.ok && !*abort_flag) {
       constexpr int kVec = kH / 4;
+      constexpr int U2 = Part<2>::U;
+      const int G2 = tiles * kMT2 * U2;
       const size_t slab = static_cast<size_t>(n_sel_pad) * kH;
       const int total = a.g.T * kVec;
       for (int i = blockIdx.x * kEpiThreads + c.etid; i < total; i += gridDim.x * kEpiThreads) {
         const int t = i / kVec, col = i % kVec;
-        combine_unit(a.o, slab, split2, __popc(fa->mask[t]), a.g.tok_rows + t * kTopK, a.g.perm_weight, col,
+        const uint32_t mask = fa->mask[t];
+        const int m = col / 32;   // weight-row tile of these four output columns
+        auto slabs = [&](int j) {   // the token's j-th row belongs to its j-th local expert (ascending)
+          uint32_t rest = mask;
+          for (int x = 0; x < j; ++x) rest &= rest - 1;
+          const int le = __ffs(rest) - 1;
+          return tile_pieces(aux->prefix[le] * kMT2 + m, U2, G2, n_ctas);
+        };
+        combine_unit(a.o, slab, slabs, __popc(mask), a.g.tok_rows + t * kTopK, a.g.perm_weight, col,
                      a.g.out_rows ? a.g.out_rows[t] : a.g.out_bf16 + static_cast<size_t>(t) * kH);
       }
     }

@@ -15,6 +15,48 @@ __device__ __forceinline__ float from_e4m3(uint8_t b) {
   return __half2float(__half(h));
 }
 
+// SwiGLU of 4 columns per lane of one (row, 128-column block), split of the result into kNTerms e4m3
+// planes with one power-of-two scale for the block.
+__device__ __forceinline__ void swiglu_finish_block(const float4 x1, const float4 x2, int row, int kb, int lane, uint8_t* cq,
+                                                    float* c_scale, int rows_cap) {
+  float c[4];
+  c[0] = __fmul_rn(x2.x / (1.0f + expf(-x2.x)), x1.x);
+  c[1] = __fmul_rn(x2.y / (1.0f + expf(-x2.y)), x1.y);
+  c[2] = __fmul_rn(x2.z / (1.0f + expf(-x2.z)), x1.z);
+  c[3] = __fmul_rn(x2.w / (1.0f + expf(-x2.w)), x1.w);
+  float amax = fmaxf(fmaxf(fabsf(c[0]), fabsf(c[1])), fmaxf(fabsf(c[2]), fabsf(c[3])));
+#pragma unroll
+  for (int d = 16; d > 0; d >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, d));
+  // power-of-two scale 2^e with amax / scale in (224, 448]: e = floor(log2(amax / 448)) + 1, clamped to
+  // [-100, 100]; read from the exponent field (a denormal quotient clamps to -100 either way)
+  int e = 0;
+  if (amax > 0.0f && amax < 3.0e38f) {
+    e = static_cast<int>((__float_as_uint(amax * (1.0f / 448.0f)) >> 23) & 0xFFu) - 127 + 1;
+    e = max(-100, min(100, e));
+  }
+  const float scale = __uint_as_float(static_cast<uint32_t>(e + 127) << 23);
+  const float inv = __uint_as_float(static_cast<uint32_t>(127 - e) << 23);
+  uint32_t packed[kNTerms];
+#pragma unroll
+  for (int t = 0; t < kNTerms; ++t) packed[t] = 0;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    float r = c[i] * inv;
+    if (!(fabsf(r) <= 448.0f)) r = r > 0.0f ? 448.0f : (r < 0.0f ? -448.0f : 0.0f);   // inf / nan guard
+#pragma unroll
+    for (int t = 0; t < kNTerms; ++t) {
+      const uint8_t q = to_e4m3(r);
+      r -= from_e4m3(q);
+      packed[t] |= static_cast<uint32_t>(q) << (8 * i);
+    }
+  }
+#pragma unroll
+  for (int t = 0; t < kNTerms; ++t)
+    *reinterpret_cast<uint32_t*>(cq + (static_cast<size_t>(t) * rows_cap + row) * kI + kb * kBlock + lane * 4) =
+        packed[t];
+  if (lane == 0) c_scale[static_cast<size_t>(row) * kKB2 + kb] = scale;
+}
+
 // SwiGLU + e4m3 split of NB consecutive 128-column blocks of one row by one warp; lane owns 4
 // columns of each block.  `g1` points at the first split-K slab; slabs are `slab` floats apart.
 // All loads of the NB blocks are issued before any arithmetic (memory-level parallelism), and they
@@ -54,50 +96,33 @@ __device__ __forceinline__ void swiglu_split_blocks(const float* g1, size_t slab
     }
   }
 #pragma unroll
-  for (int b = 0; b < NB; ++b) {
-    const int kb = kb0 + b;
-    float c[4];
-    c[0] = __fmul_rn(x2[b].x / (1.0f + expf(-x2[b].x)), x1[b].x);
-    c[1] = __fmul_rn(x2[b].y / (1.0f + expf(-x2[b].y)), x1[b].y);
-    c[2] = __fmul_rn(x2[b].z / (1.0f + expf(-x2[b].z)), x1[b].z);
-    c[3] = __fmul_rn(x2[b].w / (1.0f + expf(-x2[b].w)), x1[b].w);
-    float amax = fmaxf(fmaxf(fabsf(c[0]), fabsf(c[1])), fmaxf(fabsf(c[2]), fabsf(c[3])));
-#pragma unroll
-    for (int d = 16; d > 0; d >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, d));
-    // power-of-two scale 2^e with amax / scale in (224, 448]: e = floor(log2(amax / 448)) + 1, clamped to
-    // [-100, 100]; read from the exponent field (a denormal quotient clamps to -100 either way)
-    int e = 0;
-    if (amax > 0.0f && amax < 3.0e38f) {
-      e = static_cast<int>((__float_as_uint(amax * (1.0f / 448.0f)) >> 23) & 0xFFu) - 127 + 1;
-      e = max(-100, min(100, e));
-    }
-    const float scale = __uint_as_float(static_cast<uint32_t>(e + 127) << 23);
-    const float inv = __uint_as_float(static_cast<uint32_t>(127 - e) << 23);
-    uint32_t packed[kNTerms];
-#pragma unroll
-    for (int t = 0; t < kNTerms; ++t) packed[t] = 0;
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      float r = c[i] * inv;
-      if (!(fabsf(r) <= 448.0f)) r = r > 0.0f ? 448.0f : (r < 0.0f ? -448.0f : 0.0f);   // inf / nan guard
-#pragma unroll
-      for (int t = 0; t < kNTerms; ++t) {
-        const uint8_t q = to_e4m3(r);
-        r -= from_e4m3(q);
-        packed[t] |= static_cast<uint32_t>(q) << (8 * i);
-      }
-    }
-#pragma unroll
-    for (int t = 0; t < kNTerms; ++t)
-      *reinterpret_cast<uint32_t*>(cq + (static_cast<size_t>(t) * rows_cap + row) * kI + kb * kBlock + lane * 4) =
-          packed[t];
-    if (lane == 0) c_scale[static_cast<size_t>(row) * kKB2 + kb] = scale;
-  }
+  for (int b = 0; b < NB; ++b) swiglu_finish_block(x1[b], x2[b], row, kb0 + b, lane, cq, c_scale, rows_cap);
 }
 
 __device__ __forceinline__ void swiglu_split_unit(const float* g1, size_t slab, int split, int row, int kb, int lane,
                                                   uint8_t* cq, float* c_scale, int rows_cap) {
   swiglu_split_blocks<1>(g1, slab, split, row, kb, lane, cq, c_scale, rows_cap);
+}
+
+// The same for one block whose two halves have their own numbers of slabs (balanced partition of the
+// decode kernel): x1 = sum of n1 slabs, x2 = sum of n2 slabs, each in slab order.
+__device__ __forceinline__ void swiglu_split_unit2(const float* g1, size_t slab, int n1, int n2, int row, int kb, int lane,
+                                                   uint8_t* cq, float* c_scale, int rows_cap) {
+  constexpr int kMax = 8;
+  const float* p = g1 + static_cast<size_t>(row) * k2I + kb * kBlock + lane * 4;
+  float4 u[kMax], v[kMax];
+#pragma unroll
+  for (int s = 0; s < kMax; ++s) {
+    u[s] = s < n1 ? __ldcg(reinterpret_cast<const float4*>(p + s * slab)) : make_float4(0.f, 0.f, 0.f, 0.f);
+    v[s] = s < n2 ? __ldcg(reinterpret_cast<const float4*>(p + s * slab + kI)) : make_float4(0.f, 0.f, 0.f, 0.f);
+  }
+  float4 x1 = u[0], x2 = v[0];
+#pragma unroll
+  for (int s = 1; s < kMax; ++s) {
+    if (s < n1) { x1.x += u[s].x; x1.y += u[s].y; x1.z += u[s].z; x1.w += u[s].w; }
+    if (s < n2) { x2.x += v[s].x; x2.y += v[s].y; x2.z += v[s].z; x2.w += v[s].w; }
+  }
+  swiglu_finish_block(x1, x2, row, kb, lane, cq, c_scale, rows_cap);
 }
 
 __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
@@ -109,7 +134,9 @@ __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
 // Weighted combine of 4 output columns of one token: the token's local experts in ascending
 // order, each the sum of its GEMM2 split-K slabs, multiply then add (the definition's
 // index_add_(O * w), references/moe.py:196-200), bf16 round-to-nearest-even.
-__device__ __forceinline__ void combine_unit(const float* o, size_t slab, int split, int n_local, const int* rows,
+// `slabs(j)` gives the number of slabs of the token's j-th row.
+template <typename SlabCount>
+__device__ __forceinline__ void combine_unit(const float* o, size_t slab, SlabCount slabs, int n_local, const int* rows,
                                              const float* perm_weight, int c, uint16_t* out_row) {
   float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
   for (int j = 0; j < n_local; ++j) {
@@ -117,6 +144,7 @@ __device__ __forceinline__ void combine_unit(const float* o, size_t slab, int sp
     const float w = perm_weight[row];
     const float* p = o + static_cast<size_t>(row) * kH + c * 4;
     float4 v = __ldcg(reinterpret_cast<const float4*>(p));
+    const int split = slabs(j);
     for (int s = 1; s < split; ++s) {
       const float4 u = __ldcg(reinterpret_cast<const float4*>(p + s * slab));
       v.x += u.x; v.y += u.y; v.z += u.z; v.w += u.w;

@@ -39,17 +39,12 @@ static_assert(sizeof(Aux) <= 1024, "Aux must fit its slot");
 
 // Extra shared state of the decode-fused kernels: every CTA routes all (<= 16) tokens itself.
 struct FusedAux {
-  uint32_t keys[kEGlobal];            // order-preserving keys of the biased scores of the token being routed
-  float sval[kEGlobal];               // its unbiased sigmoid scores
-  float gscore[kNGroup];
-  int selidx[kTopK];
-  float sels[kTopK];
-  int tidx[kFusedMaxTokens][kTopK];
-  float tw[kFusedMaxTokens][kTopK];
+  float sval[kEGlobal];               // routing bias as fp32
+  int tidx[kFusedMaxTokens][kTopK];   // selection of every token (global expert ids, descending score)
+  float tw[kFusedMaxTokens][kTopK];   // and its combination weights
   uint32_t mask[kFusedMaxTokens];     // per token: selected local experts
   uint32_t colmask[kELocal];          // per local expert: tokens that selected it
-  int items, split, n_sel_pad, n_sel;      // GEMM1 items / split-K factor, slab stride, rows
-  int items2, split2;                      // GEMM2 items / split-K factor
+  int tiles, n_sel_pad, n_sel;        // active experts (one token tile each), slab stride, rows
 };
 static_assert(sizeof(FusedAux) <= 4096, "FusedAux must fit its slot");
 
@@ -110,7 +105,7 @@ __device__ __forceinline__ bool grid_barrier_wait(unsigned int* word2, unsigned 
   }
 }
 
-// K-blocks per pipeline stage of the 16-token kernels of both GEMMs (split-K granularity).
+// K-blocks per pipeline stage of the decode kernel.
 constexpr int kDecodeKps = 2;
 
 // CPW fp32 columns of this warp's 32 TMEM lanes -> registers.
@@ -134,102 +129,121 @@ __device__ __forceinline__ void decode_route_schedule(const GemmArgs& a, uint8_t
                                                       MoeSched* sched) {
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  if (a.T <= 2) {
-    // Block-cooperative routing (same arithmetic and tie rules as route_token): thread e < 256 owns
-    // expert e, so warp g is routing group g.  Per token: sigmoid + bias, the group's two best by
-    // two warp reductions, then every kept expert counts how many kept experts beat it; the eight
-    // with rank < 8 are the selection in descending order.  ~1k cycles per token instead of the
-    // ~7k of one warp doing eight rounds of arg-max.
-    const int e = threadIdx.x;
-    float* xs = reinterpret_cast<float*>(smem);                 // [T][256] logits; the stage ring is still idle
-    float bias_e = 0.0f;
-    if (e < kEGlobal) {
-      bias_e = __uint_as_float(static_cast<uint32_t>(a.bias_bf16[e]) << 16);
-      for (int t = 0; t < a.T; ++t) xs[t * kEGlobal + e] = a.logits[static_cast<size_t>(t) * kEGlobal + e];
+  // Routing in two steps (same arithmetic and tie rules as route_token; the work is spread over all warps and
+  // the instruction count per token is a third).  Step A, one warp per (token, routing group), lane = expert:
+  // sigmoid + bias -> key (kept in shared memory with the unbiased score), two rounds of warp arg-max for the
+  // group score.  Step B, one warp per token: the four best groups, then every lane holds its expert of each
+  // kept group and eight rounds of arg-max over the 128 candidates give the selection in descending order.
+  uint32_t* skey = reinterpret_cast<uint32_t*>(smem);             // [T][256] keys; the stage ring is still idle
+  float* sval = reinterpret_cast<float*>(smem) + kFusedMaxTokens * kEGlobal;      // [T][256] unbiased scores
+  float* gsc = reinterpret_cast<float*>(smem) + 2 * kFusedMaxTokens * kEGlobal;   // [T][8]   group scores
+  float* bias_s = fa->sval;
+  for (int i = threadIdx.x; i < kEGlobal; i += kGemmThreads)
+    bias_s[i] = __uint_as_float(static_cast<uint32_t>(a.bias_bf16[i]) << 16);
+  constexpr int kWarps = kGemmThreads / 32;
+  constexpr int kMaxUnits = (kFusedMaxTokens * kNGroup + kWarps - 1) / kWarps;
+  const int units = a.T * kNGroup;
+  float x[kMaxUnits];
+#pragma unroll
+  for (int i = 0; i < kMaxUnits; ++i) {                            // all logits of this warp's units in flight
+    const int u = warp + i * kWarps;
+    x[i] = u < units ? a.logits[static_cast<size_t>(u) * 32 + lane] : 0.0f;      // [t][g][lane] = [u][lane]
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) MOE_ROUTE_TRACE(0);
+#pragma unroll
+  for (int i = 0; i < kMaxUnits; ++i) {
+    const int u = warp + i * kWarps;
+    if (u < units) {                                               // uniform over the warp
+      const float s = 1.0f / (1.0f + expf(-x[i]));
+      const uint32_t key = order_key(s + bias_s[(u & 7) * 32 + lane]);
+      skey[u * 32 + lane] = key;
+      sval[u * 32 + lane] = s;
+      // group score = best + second best biased score (ties: any; undo the order-preserving map)
+      const uint32_t k1 = __reduce_max_sync(0xFFFFFFFFu, key);
+      const int first = __ffs(__ballot_sync(0xFFFFFFFFu, key == k1)) - 1;
+      const uint32_t k2 = __reduce_max_sync(0xFFFFFFFFu, lane == first ? 0u : key);
+      const uint32_t u1 = (k1 & 0x80000000u) ? (k1 & 0x7FFFFFFFu) : ~k1;
+      const uint32_t u2 = (k2 & 0x80000000u) ? (k2 & 0x7FFFFFFFu) : ~k2;
+      if (lane == 0) gsc[u] = __uint_as_float(u1) + __uint_as_float(u2);
     }
-    if (threadIdx.x == 0) MOE_ROUTE_TRACE(0);
-    for (int t = 0; t < a.T; ++t) {
-      float s_e = 0.0f;
-      uint32_t key_e = 0;
-      if (e < kEGlobal) {
-        s_e = 1.0f / (1.0f + expf(-xs[t * kEGlobal + e]));
-        key_e = order_key(s_e + bias_e);
-        fa->keys[e] = key_e;
-        fa->sval[e] = s_e;
-        const uint32_t k1 = __reduce_max_sync(0xFFFFFFFFu, key_e);
-        const int first = __ffs(__ballot_sync(0xFFFFFFFFu, key_e == k1)) - 1;
-        const uint32_t k2 = __reduce_max_sync(0xFFFFFFFFu, lane == first ? 0u : key_e);
-        const uint32_t u1 = (k1 & 0x80000000u) ? (k1 & 0x7FFFFFFFu) : ~k1;
-        const uint32_t u2 = (k2 & 0x80000000u) ? (k2 & 0x7FFFFFFFu) : ~k2;
-        if (lane == 0) fa->gscore[warp] = __uint_as_float(u1) + __uint_as_float(u2);
-      }
-      __syncthreads();
-      if (e < kEGlobal) {
-        uint32_t keep = 0;
+  }
+  __syncthreads();
+  // Step B for up to two tokens per warp (t and t + kWarps), interleaved: the rounds of a token are a
+  // dependent chain of warp reductions, those of two tokens are independent.
+  {
+    constexpr int kTok = (kFusedMaxTokens + kWarps - 1) / kWarps;   // 2
+    uint32_t kq[kTok][kTopKGroup];
+    int gq[kTok][kTopKGroup];
+    float sel_s[kTok], sum[kTok];
+    int sel_idx[kTok];
 #pragma unroll
-        for (int g = 0; g < kNGroup; ++g) {
-          int rank = 0;
+    for (int b = 0; b < kTok; ++b) {
+      const int t = warp + b * kWarps;
+      sel_s[b] = sum[b] = 0.0f;
+      sel_idx[b] = 0;
+      if (t < a.T) {
+        // the four best groups (ties: lower group first), ascending in gq
+        const float gs = gsc[t * kNGroup + (lane & 7)];
+        int grank = 0;
 #pragma unroll
-          for (int h2 = 0; h2 < kNGroup; ++h2)
-            rank += (fa->gscore[h2] > fa->gscore[g]) || (fa->gscore[h2] == fa->gscore[g] && h2 < g);
-          keep |= (rank < kTopKGroup ? 1u : 0u) << g;
+        for (int h = 0; h < kNGroup; ++h) {
+          const float gh = __shfl_sync(0xFFFFFFFFu, gs, h);
+          grank += (gh > gs) || (gh == gs && h < (lane & 7));
         }
-        if ((keep >> warp) & 1u) {
-          int rank = 0;
-          for (int g = 0; g < kNGroup; ++g) {
-            if (!((keep >> g) & 1u)) continue;
-            const uint4* kv = reinterpret_cast<const uint4*>(fa->keys + g * 32);
+        uint32_t keep = __ballot_sync(0xFFFFFFFFu, lane < kNGroup && grank < kTopKGroup);
 #pragma unroll
-            for (int c = 0; c < 8; ++c) {
-              const uint4 k = kv[c];
-              const int j = g * 32 + c * 4;
-              rank += (k.x > key_e) || (k.x == key_e && j + 0 < e);
-              rank += (k.y > key_e) || (k.y == key_e && j + 1 < e);
-              rank += (k.z > key_e) || (k.z == key_e && j + 2 < e);
-              rank += (k.w > key_e) || (k.w == key_e && j + 3 < e);
-            }
+        for (int q = 0; q < kTopKGroup; ++q) {
+          gq[b][q] = __ffs(keep) - 1;
+          keep &= keep - 1;
+          kq[b][q] = skey[t * kEGlobal + gq[b][q] * 32 + lane];
+        }
+      }
+    }
+#pragma unroll
+    for (int r = 0; r < kTopK; ++r) {
+#pragma unroll
+      for (int b = 0; b < kTok; ++b) {
+        const int t = warp + b * kWarps;
+        if (t < a.T) {
+          // this lane's best candidate (ties: lower group), then the warp's (ties: lower expert index)
+          uint32_t best = kq[b][0];
+          int bq = 0;
+#pragma unroll
+          for (int q = 1; q < kTopKGroup; ++q)
+            if (kq[b][q] > best) { best = kq[b][q]; bq = q; }
+          const uint32_t m = __reduce_max_sync(0xFFFFFFFFu, best);
+          const uint32_t win = __reduce_min_sync(0xFFFFFFFFu, best == m ? static_cast<uint32_t>(bq * 32 + lane) : 0xFFFFFFFFu);
+          const int wq = win >> 5, wl = win & 31;
+          int wg = gq[b][0];
+#pragma unroll
+          for (int q = 1; q < kTopKGroup; ++q) wg = (q == wq) ? gq[b][q] : wg;
+          const int idx = wg * 32 + wl;
+          const float sk = sval[t * kEGlobal + idx];
+          sum[b] += sk;                                  // the normaliser is summed in selection order
+          if (lane == r) { sel_s[b] = sk; sel_idx[b] = idx; }
+          if (lane == wl) {
+#pragma unroll
+            for (int q = 0; q < kTopKGroup; ++q) kq[b][q] = (q == wq) ? 0u : kq[b][q];   // taken: below every real key
           }
-          if (rank < kTopK) { fa->selidx[rank] = e; fa->sels[rank] = s_e; }
         }
       }
-      __syncthreads();
-      if (warp == 0) {
-        const float sv = lane < kTopK ? fa->sels[lane] : 0.0f;
-        float sum = 0.0f;
+    }
 #pragma unroll
-        for (int k = 0; k < kTopK; ++k) sum += __shfl_sync(0xFFFFFFFFu, sv, k);
-        sum += 1e-20f;
+    for (int b = 0; b < kTok; ++b) {
+      const int t = warp + b * kWarps;
+      if (t < a.T) {
+        const float total = sum[b] + 1e-20f;
         uint32_t bit = 0;
         if (lane < kTopK) {
-          const int idx = fa->selidx[lane];
-          fa->tidx[t][lane] = idx;
-          fa->tw[t][lane] = (sv / sum) * a.routed_scaling_factor;
-          const int le = idx - a.local_expert_offset;
+          fa->tidx[t][lane] = sel_idx[b];
+          fa->tw[t][lane] = (sel_s[b] / total) * a.routed_scaling_factor;
+          const int le = sel_idx[b] - a.local_expert_offset;
           if (le >= 0 && le < kELocal) bit = 1u << le;
         }
         bit = __reduce_or_sync(0xFFFFFFFFu, bit);
         if (lane == 0) fa->mask[t] = bit;
       }
-    }
-  } else {
-    // More than two tokens: one warp per token (ten at a time), each doing the warp-level routing.
-    float* bias_s = fa->sval;                                  // 256 floats, free on this path
-    for (int i = threadIdx.x; i < kEGlobal; i += kGemmThreads)
-      bias_s[i] = __uint_as_float(static_cast<uint32_t>(a.bias_bf16[i]) << 16);
-    __syncthreads();
-    for (int t = warp; t < a.T; t += kGemmThreads / 32) {
-      int idx;
-      float w;
-      route_token(a.logits + static_cast<size_t>(t) * kEGlobal, bias_s, a.routed_scaling_factor, lane, idx, w);
-      uint32_t bit = 0;
-      if (lane < kTopK) {
-        fa->tidx[t][lane] = idx;
-        fa->tw[t][lane] = w;
-        const int le = idx - a.local_expert_offset;
-        if (le >= 0 && le < kELocal) bit = 1u << le;
-      }
-      bit = __reduce_or_sync(0xFFFFFFFFu, bit);
-      if (lane == 0) fa->mask[t] = bit;
     }
   }
   if (threadIdx.x == 0) MOE_ROUTE_TRACE(1);
@@ -252,19 +266,12 @@ __device__ __forceinline__ void decode_route_schedule(const GemmArgs& a, uint8_t
     const uint32_t act = __ballot_sync(0xFFFFFFFFu, c > 0);
     const int n_sel = __shfl_sync(0xFFFFFFFFu, inc, 31), tiles_total = __shfl_sync(0xFFFFFFFFu, tinc, 31);
     const int pad = (n_sel + 15) & ~15;
-    const int s1 = choose_split_warp(tiles_total * kMT1, kMaxSplit1, a.ctas, pad, a.slab_rows, lane, kKB1,
-                                     kDecodeKps);
-    const int s2 = choose_split_warp(tiles_total * kMT2, kMaxSplit2, a.ctas, pad, a.slab_rows, lane, kKB2,
-                                     kDecodeKps);
     if (lane == 0) {
       aux->offs[0] = 0;
       aux->prefix[0] = 0;
-      fa->items = tiles_total * kMT1 * s1;
-      fa->split = s1;
+      fa->tiles = tiles_total;
       fa->n_sel_pad = pad;
       fa->n_sel = n_sel;
-      fa->items2 = tiles_total * kMT2 * s2;
-      fa->split2 = s2;
     }
     if (blockIdx.x == 0) {
       sched->counts[lane] = c;
@@ -282,10 +289,11 @@ __device__ __forceinline__ void decode_route_schedule(const GemmArgs& a, uint8_t
         sched->n_active = __popc(act);
         sched->n_tile = kFusedMaxTokens;
         sched->tiles_total = tiles_total;
-        sched->split1 = s1;
-        sched->split2 = s2;
-        sched->items1 = tiles_total * kMT1 * s1;
-        sched->items2 = tiles_total * kMT2 * s2;
+        sched->split1 = 0;
+        sched->split2 = 0;
+        sched->items1 = tiles_total * kMT1 * (kKB1 / kDecodeKps);
+        sched->items2 = tiles_total * kMT2 * (kKB2 / kDecodeKps);
+        sched->ctas = static_cast<int>(gridDim.x);
       }
     }
   }

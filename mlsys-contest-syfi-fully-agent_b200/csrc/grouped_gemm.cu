@@ -77,7 +77,7 @@ struct Cfg {
   static constexpr int STAGE_BYTES = KPS * KB_BYTES;
   static constexpr int SC_BUFS = N_TILE <= 32 ? 2 : 1;                  // scale-product tables
   static constexpr int SC_BYTES = SC_BUFS * KB * N_TILE * 4;
-  static constexpr int AUX_BYTES = 1024 + 4096;                         // Aux + FusedAux
+  static constexpr int AUX_BYTES = 1024;
   static constexpr int BUDGET = 227 * 1024 - 1024;   // 1 KB slack for the 1024-byte alignment of the ring
   static constexpr int STAGES_FIT = (BUDGET - SC_BYTES - AUX_BYTES) / STAGE_BYTES;
   static constexpr int STAGES = STAGES_FIT > 10 ? 10 : STAGES_FIT;
@@ -130,7 +130,7 @@ __device__ __forceinline__ Item decode_item(int i, int split, const Aux* aux) {
   return it;
 }
 
-template <int GEMM, int N_TILE, bool FUSED = false>
+template <int GEMM, int N_TILE>
 __global__ void __launch_bounds__(kThreads, 1)
 grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_b, GemmArgs a) {
   using C = Cfg<GEMM, N_TILE>;
@@ -163,24 +163,13 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
   }
   griddep_wait();   // the schedule, the operands and the output slabs belong to earlier kernels until here
   if (threadIdx.x == 0) TRACE(3, 5);
-  if (FUSED && blockIdx.x == 0 && threadIdx.x == 0) grid_barrier_init(GEMM == 1 ? sched->bar1 : sched->bar2, a.call_tag);
   int items, split, n_sel_pad;
-  FusedAux* fa = reinterpret_cast<FusedAux*>(reinterpret_cast<uint8_t*>(aux) + 1024);
-  if constexpr (FUSED && GEMM == 1) {
-    static_assert(N_TILE == kFusedMaxTokens, "the fused path puts every token in one token tile");
-    static_assert(Cfg<1, N_TILE>::KPS == kDecodeKps && Cfg<2, N_TILE>::KPS == kDecodeKps, "split-K granularity");
-    decode_route_schedule(a, smem, aux, fa, sched);
-    items = fa->items;
-    split = fa->split;
-    n_sel_pad = fa->n_sel_pad;
-  } else {
-    items = GEMM == 1 ? sched->items1 : sched->items2;
-    split = GEMM == 1 ? sched->split1 : sched->split2;
-    n_sel_pad = sched->n_sel_pad;
-    if (threadIdx.x <= kELocal) {
-      aux->prefix[threadIdx.x] = GEMM == 1 ? sched->tile_prefix[threadIdx.x] : sched->tile_prefix2[threadIdx.x];
-      aux->offs[threadIdx.x] = sched->offs[threadIdx.x];
-    }
+  items = GEMM == 1 ? sched->items1 : sched->items2;
+  split = GEMM == 1 ? sched->split1 : sched->split2;
+  n_sel_pad = sched->n_sel_pad;
+  if (threadIdx.x <= kELocal) {
+    aux->prefix[threadIdx.x] = GEMM == 1 ? sched->tile_prefix[threadIdx.x] : sched->tile_prefix2[threadIdx.x];
+    aux->offs[threadIdx.x] = sched->offs[threadIdx.x];
   }
   tc_fence_before_sync();
   __syncthreads();
@@ -201,7 +190,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
       for (int i = blockIdx.x; ok && i < items; i += gridDim.x) {
         const Item w = decode_item<GEMM, N_TILE>(i, split, aux);
         const int wy = w.e * C::M_TOTAL + w.m * 128;
-        const int by = (FUSED && GEMM == 1) ? 0 : w.row0;
+        const int by = w.row0;
         for (int kb = w.kb0; kb < w.kb1; kb += C::KPS) {
           if (!mbar_wait(done_base + stage * 8, ph ^ 1u, abort_flag)) { ok = false; break; }
           const uint32_t bar = full_base + stage * 8;
@@ -284,10 +273,6 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
       if (idx >= nkb * N_TILE) return 0.0f;
       const int kbl = idx / N_TILE, j = idx % N_TILE, kb = w.kb0 + kbl;
       const float ws = __ldg(a.w_scale + (static_cast<size_t>(w.e) * C::MT + w.m) * C::KB + kb);
-      if constexpr (FUSED && GEMM == 1) {      // column j is token j; the scale table is the definition's [56, T]
-        if (!((fa->colmask[w.e] >> j) & 1u)) return 0.0f;
-        return ws * __ldg(a.hidden_scale + static_cast<size_t>(kb) * a.T + j);
-      }
       if (j >= w.valid) return 0.0f;
       return ws * __ldg(a.b_scale + static_cast<size_t>(w.row0 + j) * C::KB + kb);
     };
@@ -366,55 +351,17 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
         if (++buf == C::NBUF) { buf = 0; bph ^= 1u; }
       }
       if (!ok) break;
-      if constexpr (FUSED && GEMM == 1) {      // token columns -> the expert's rows (ascending token)
-        const uint32_t cm = fa->colmask[w.e];
-        float* out = a.out + (static_cast<size_t>(w.s) * n_sel_pad + w.row0) * C::M_TOTAL + w.m * 128 + q * 32 + lane;
+      float* out = a.out + (static_cast<size_t>(w.s) * n_sel_pad + w.row0 + h * C::CPW) * C::M_TOTAL + w.m * 128 +
+                   q * 32 + lane;
 #pragma unroll
-        for (int j = 0; j < C::CPW; ++j) {
-          const int col = h * C::CPW + j;
-          if ((cm >> col) & 1u) out[static_cast<size_t>(__popc(cm & ((1u << col) - 1u))) * C::M_TOTAL] = acc[j];
-        }
-      } else {
-        float* out = a.out + (static_cast<size_t>(w.s) * n_sel_pad + w.row0 + h * C::CPW) * C::M_TOTAL + w.m * 128 +
-                     q * 32 + lane;
-#pragma unroll
-        for (int j = 0; j < C::CPW; ++j)
-          if (h * C::CPW + j < w.valid) out[static_cast<size_t>(j) * C::M_TOTAL] = acc[j];
-      }
+      for (int j = 0; j < C::CPW; ++j)
+        if (h * C::CPW + j < w.valid) out[static_cast<size_t>(j) * C::M_TOTAL] = acc[j];
       if (C::SC_BUFS == 2 && inext < items) {
         float* scn = sc_base + ((nitem + 1) & 1u) * (C::KB * N_TILE);
 #pragma unroll
         for (int x = 0; x < kMaxE; ++x) {
           const int idx = etid + x * kEpiThreads;
           if (idx < C::KB * N_TILE) scn[idx] = pre[x];
-        }
-      }
-    }
-    if constexpr (FUSED) {
-      // Tail phase of the decode path.  All CTAs are resident (one per SM), so a grid barrier is safe;
-      // after it every split-K slab of this GEMM is complete and the next stage runs here instead of
-      // in a kernel of its own: SwiGLU + e4m3 split after GEMM1, weighted combine + bf16 cast after GEMM2.
-      __threadfence();
-      epi_sync();
-      if (etid == 0) TRACE(3, 3);
-      if (ok && etid == 0 && !grid_barrier(GEMM == 1 ? sched->bar1 : sched->bar2, a.call_tag, gridDim.x)) *abort_flag = 1;
-      epi_sync();
-      if (etid == 0) TRACE(3, 4);
-      if (ok && !*abort_flag) {
-        if constexpr (GEMM == 1) {
-          const int units = fa->n_sel * kKB2;
-          const size_t slab = static_cast<size_t>(n_sel_pad) * k2I;
-          for (int u = blockIdx.x * kEpiWarps + (warp - kFirstEpiWarp); u < units; u += gridDim.x * kEpiWarps)
-            swiglu_split_unit(a.out, slab, split, u / kKB2, u % kKB2, lane, a.cq, a.c_scale, a.rows_cap);
-        } else {
-          constexpr int kVec = kH / 4;
-          const size_t slab = static_cast<size_t>(n_sel_pad) * kH;
-          const int total = a.T * kVec;
-          for (int i = blockIdx.x * kEpiThreads + etid; i < total; i += gridDim.x * kEpiThreads) {
-            const int t = i / kVec, c = i % kVec;
-            combine_unit(a.out, slab, split, __popc(a.local_mask[t]), a.tok_rows + t * kTopK, a.perm_weight, c,
-                         a.out_rows ? a.out_rows[t] : a.out_bf16 + static_cast<size_t>(t) * kH);
-          }
         }
       }
     }
@@ -438,20 +385,6 @@ int launch_one(const CUtensorMap& tm_w, const CUtensorMap& tm_b, const GemmArgs&
   using C = Cfg<GEMM, N_TILE>;
   return static_cast<int>(launch_pdl(grouped_gemm_kernel<GEMM, N_TILE>, dim3(ctas), dim3(kThreads), C::SMEM_BYTES,
                                      stream, tm_w, tm_b, a));
-}
-
-template <int GEMM>
-int launch_fused(const CUtensorMap& tm_w, const CUtensorMap& tm_b, const GemmArgs& a, int ctas, cudaStream_t stream) {
-  using C = Cfg<GEMM, kFusedMaxTokens>;
-  return static_cast<int>(launch_pdl(grouped_gemm_kernel<GEMM, kFusedMaxTokens, true>, dim3(ctas), dim3(kThreads),
-                                     C::SMEM_BYTES, stream, tm_w, tm_b, a));
-}
-
-template <int GEMM>
-int init_fused() {
-  using C = Cfg<GEMM, kFusedMaxTokens>;
-  return static_cast<int>(cudaFuncSetAttribute(grouped_gemm_kernel<GEMM, kFusedMaxTokens, true>,
-                                               cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES));
 }
 
 template <int GEMM, int N_TILE>
@@ -489,14 +422,7 @@ int grouped_gemm_init() {
   if ((rc = init_one<2, 32>())) return rc;
   if ((rc = init_one<2, 64>())) return rc;
   if ((rc = init_one<2, 128>())) return rc;
-  if ((rc = init_fused<1>())) return rc;
-  if ((rc = init_fused<2>())) return rc;
   return 0;
-}
-
-int launch_fused_gemm(int gemm_id, const CUtensorMap& tm_w, const CUtensorMap& tm_b, const GemmArgs& a, int ctas,
-                      cudaStream_t stream) {
-  return gemm_id == 1 ? launch_fused<1>(tm_w, tm_b, a, ctas, stream) : launch_fused<2>(tm_w, tm_b, a, ctas, stream);
 }
 
 int launch_grouped_gemm(int gemm_id, int n_tile, const CUtensorMap& tm_w, const CUtensorMap& tm_b, const GemmArgs& a,

@@ -82,7 +82,7 @@ struct GemmArgs {
   const float* w_scale;         // [32, M/128, K/128]
   const float* b_scale;         // per-row scales, row-major: GEMM1 [rows, 56]; GEMM2 [rows, 16]
   float* out;                   // fp32 slabs [split][n_sel_pad, M]
-  // ---- only read by the decode-fused kernels (T <= 16), see grouped_gemm.cu
+  // ---- only read by the single-launch decode kernel (T <= 16), see decode_kernel.cu
   const float* logits;          // [T, 256]
   const uint16_t* bias_bf16;    // [256]
   const float* hidden_scale;    // [56, T]
@@ -92,8 +92,8 @@ struct GemmArgs {
   unsigned int call_tag;        // distinct per call: tags the grid barrier words
   int* topk_idx; float* topk_w; uint32_t* local_mask;
   int* perm_token; float* perm_weight; int* tok_rows;
-  uint8_t* cq; float* c_scale;  // SwiGLU planes written by the fused GEMM1 tail
-  uint16_t* out_bf16;           // final output written by the fused GEMM2 tail
+  uint8_t* cq; float* c_scale;  // SwiGLU planes and their scales
+  uint16_t* out_bf16;           // final output
   uint16_t* const* out_rows;    // optional per-token destinations instead of out_bf16 (may be peer memory)
 };
 
@@ -122,9 +122,6 @@ void launch_gather_rows(const GatherArgs& a, int T, cudaStream_t stream);
 // gemm_id 1 or 2; n_tile in {16, 32, 64, 128} (GEMM1 also 256).  Returns a cudaError_t as int.
 int launch_grouped_gemm(int gemm_id, int n_tile, const CUtensorMap& tm_w, const CUtensorMap& tm_b, const GemmArgs& a,
                         int ctas, cudaStream_t stream);
-// Decode path (T <= 16): GEMM1 with in-kernel routing and a SwiGLU tail, GEMM2 with a combine tail.
-int launch_fused_gemm(int gemm_id, const CUtensorMap& tm_w, const CUtensorMap& tm_b, const GemmArgs& a, int ctas,
-                      cudaStream_t stream);
 constexpr int kFusedMaxTokens = 16;
 // Decode path in one launch: routing, GEMM1, SwiGLU, GEMM2 and combine (decode_kernel.cu).  `g` is the GEMM1 view
 // of the arguments with all routing / tail fields set; tm_x maps hidden_states, tm_c the SwiGLU planes.

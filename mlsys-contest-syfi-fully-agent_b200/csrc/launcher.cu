@@ -198,8 +198,7 @@ int pick_n_tile(int T) {
   return T <= 16 ? 16 : T <= 32 ? 32 : T <= 64 ? 64 : 128;
 }
 
-// Decode path selection (MOE_B200_FUSED_DECODE): 1 = one launch (default), 2 = two launches (a fused
-// kernel per GEMM), 0 = the general seven-kernel path.
+// Decode path selection (MOE_B200_FUSED_DECODE): 1 = one launch (default), 0 = the general multi-kernel path.
 int fused_decode_mode() {
   static const int mode = [] {
     const char* s = std::getenv("MOE_B200_FUSED_DECODE");
@@ -298,8 +297,8 @@ static int run_impl(const float* routing_logits, const uint16_t* routing_bias, c
   if ((rc = get_map(dev, planes_map(cq, L.rows_cap, n_tile2, kps2), &tm_c))) return rc;
 
   if (T <= kFusedMaxTokens && fused_decode_mode() != 0) {
-    // Decode path: two launches.  GEMM1 routes in-kernel, reads the token rows straight from
-    // hidden_states (all tokens are one token tile) and ends with SwiGLU; GEMM2 ends with the combine.
+    // Decode path: one launch.  The kernel routes, reads the token rows straight from hidden_states (all
+    // tokens are one token tile), and runs both GEMMs with the SwiGLU and combine phases in between and after.
     static std::atomic<unsigned int> call_counter{0x9E3779B1u};
     CUtensorMap tm_h;
     if ((rc = get_map(dev, kblock_map(hidden_states, static_cast<uint64_t>(T), kH, kFusedMaxTokens, kps1), &tm_h)))
@@ -313,24 +312,13 @@ static int run_impl(const float* routing_logits, const uint16_t* routing_bias, c
     fa.topk_idx = topk_idx; fa.topk_w = topk_w; fa.local_mask = local_mask;
     fa.perm_token = perm_token; fa.perm_weight = perm_weight; fa.tok_rows = tok_rows;
     fa.cq = cq; fa.c_scale = c_scale; fa.out_bf16 = output; fa.out_rows = output_rows;
-    if (fused_decode_mode() == 1) {
-      stage_mark(0, stream); stage_mark(1, stream); stage_mark(2, stream);
-      if ((rc = launch_decode(tm_w13, tm_h, tm_w2, tm_c, fa, gemm2_weights_scale, o, ctas, stream))) {
-        g_last_cuda_error = rc;
-        return MOE_B200_ECUDA;
-      }
-      stage_mark(3, stream); stage_mark(4, stream); stage_mark(5, stream); stage_mark(6, stream);
-      g_launches += 1;
-      return MOE_B200_OK;
-    }
     stage_mark(0, stream); stage_mark(1, stream); stage_mark(2, stream);
-    if ((rc = launch_fused_gemm(1, tm_w13, tm_h, fa, ctas, stream))) { g_last_cuda_error = rc; return MOE_B200_ECUDA; }
-    stage_mark(3, stream); stage_mark(4, stream);
-    GemmArgs fb = fa;
-    fb.w_scale = gemm2_weights_scale; fb.b_scale = c_scale; fb.out = o;
-    if ((rc = launch_fused_gemm(2, tm_w2, tm_c, fb, ctas, stream))) { g_last_cuda_error = rc; return MOE_B200_ECUDA; }
-    stage_mark(5, stream); stage_mark(6, stream);
-    g_launches += 2;
+    if ((rc = launch_decode(tm_w13, tm_h, tm_w2, tm_c, fa, gemm2_weights_scale, o, ctas, stream))) {
+      g_last_cuda_error = rc;
+      return MOE_B200_ECUDA;
+    }
+    stage_mark(3, stream); stage_mark(4, stream); stage_mark(5, stream); stage_mark(6, stream);
+    g_launches += 1;
     return MOE_B200_OK;
   }
 

@@ -45,12 +45,12 @@ struct MoeSched {
   int n_active;            // local experts with at least one token
   int n_tile;              // token-tile width the GEMMs were scheduled for
   int tiles_total;         // sum over experts of ceil(count / n_tile)
-  int split1, split2;      // split-K factors chosen for GEMM1 / GEMM2
-  int items1, items2;      // work items of GEMM1 / GEMM2
-  unsigned int bar1[2];    // grid barrier of the fused GEMM1 kernel: {arrivals, call tag}
-  unsigned int bar2[2];    // same for the fused GEMM2 kernel
+  int split1, split2;      // split-K factors chosen for GEMM1 / GEMM2 (0: balanced partition of the decode path)
+  int items1, items2;      // work items of GEMM1 / GEMM2 (decode path: pipeline stages)
+  unsigned int bar1[2];    // grid barrier of the decode kernel: {arrivals, call tag}
+  unsigned int bar2[2];    // spare
   int n_tile2;             // token-tile width of GEMM2 (<= n_tile)
-  int pad_[1];
+  int ctas;                // persistent CTAs of the launch that wrote this block (decode path; else 0)
   int counts[kELocal];
   int offs[kELocal + 1];       // exclusive prefix of counts
   int tile_prefix[kELocal + 1];  // exclusive prefix of GEMM1 token tiles (width n_tile)

@@ -141,6 +141,7 @@ __device__ void permute_block(const PermuteArgs& a) {
       sc->tile_prefix[0] = 0;
       sc->tile_prefix2[0] = 0;
       sc->n_tile2 = a.n_tile2;
+      sc->ctas = 0;
       sc->status = (n_sel > a.rows_cap) ? kErrSchedOverflow : 0;
       sc->n_sel = n_sel;
       sc->n_sel_pad = n_sel_pad;

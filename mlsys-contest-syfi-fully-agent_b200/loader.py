@@ -47,7 +47,7 @@ class Layout(ctypes.Structure):
 class Sched(ctypes.Structure):
     _fields_ = [(n, ctypes.c_int32) for n in ("status", "n_sel", "n_sel_pad", "n_active", "n_tile", "tiles_total",
                                               "split1", "split2", "items1", "items2")] + \
-               [("bar1", ctypes.c_uint32 * 2), ("bar2", ctypes.c_uint32 * 2), ("n_tile2", ctypes.c_int32), ("pad_", ctypes.c_int32 * 1), ("counts", ctypes.c_int32 * 32), ("offs", ctypes.c_int32 * 33),
+               [("bar1", ctypes.c_uint32 * 2), ("bar2", ctypes.c_uint32 * 2), ("n_tile2", ctypes.c_int32), ("ctas", ctypes.c_int32), ("counts", ctypes.c_int32 * 32), ("offs", ctypes.c_int32 * 33),
                 ("tile_prefix", ctypes.c_int32 * 33), ("tile_prefix2", ctypes.c_int32 * 33)]
 
 

@@ -211,6 +211,33 @@ def kernel_status(workspace: Optional[Workspace] = None, device=None) -> int:
     return st.value
 
 
+def _sum_slabs(arr, offset, sched, gemm, pad, width):
+    """fp32 result [pad, width] of one GEMM from its split-K slabs.  General path: `split` equal slabs.
+    Decode path (split == 0): a weight-row tile has as many slabs as the balanced partition cut it into
+    pieces (csrc/decode_kernel.cu: stage_owner / tile_pieces), computed here from the tile index alone."""
+    split = sched.split1 if gemm == 1 else sched.split2
+    if split > 0:
+        s = arr(offset, split * pad * width * 4, torch.float32, (split, pad, width))
+        return s.sum(dim=0) if split > 1 else s[0]
+    n, mt = sched.ctas, width // 128
+    u = (56 if gemm == 1 else 16) // 2                 # pipeline stages per tile
+    G = sched.tiles_total * mt * u
+    owner = lambda g: ((g + 1) * n - 1) // G
+    pieces = lambda tau: owner(tau * u + u - 1) - owner(tau * u) + 1
+    counts, offs = list(sched.counts), list(sched.offs)
+    active = [e for e in range(32) if counts[e] > 0]
+    smax = max(pieces(t) for t in range(len(active) * mt))
+    s = arr(offset, smax * pad * width * 4, torch.float32, (smax, pad, width))
+    res = torch.zeros(pad, width, dtype=torch.float32, device=s.device)
+    for ordinal, e in enumerate(active):
+        rows = slice(offs[e], offs[e + 1])
+        for m in range(mt):
+            cols = slice(m * 128, (m + 1) * 128)
+            for k in range(pieces(ordinal * mt + m)):   # slab order, as the kernel sums
+                res[rows, cols] += s[k, rows, cols]
+    return res
+
+
 def intermediates(T: int, workspace: Optional[Workspace] = None, device=None) -> dict:
     """Host copies of the selection / permutation / per-stage arrays the last
     call with ``T`` tokens left in the workspace (for parity tests)."""
@@ -236,10 +263,8 @@ def intermediates(T: int, workspace: Optional[Workspace] = None, device=None) ->
         tok_rows=arr(L.tok_rows, T * 8 * 4, torch.int32, (T, 8)).cpu(),
     )
     if n_sel > 0:
-        g1 = arr(L.g1, sched.split1 * pad * 4096 * 4, torch.float32, (sched.split1, pad, 4096))
-        out["g1"] = g1.sum(dim=0)[:n_sel].cpu() if sched.split1 > 1 else g1[0, :n_sel].cpu()
-        o = arr(L.o, sched.split2 * pad * H * 4, torch.float32, (sched.split2, pad, H))
-        out["o"] = o.sum(dim=0)[:n_sel].cpu() if sched.split2 > 1 else o[0, :n_sel].cpu()
+        out["g1"] = _sum_slabs(arr, L.g1, sched, 1, pad, 4096)[:n_sel].cpu()
+        out["o"] = _sum_slabs(arr, L.o, sched, 2, pad, H)[:n_sel].cpu()
         cq = arr(L.cq, L.n_terms * L.rows_cap * I, torch.float8_e4m3fn, (L.n_terms, L.rows_cap, I))[:, :n_sel]
         cs = arr(L.c_scale, L.rows_cap * 16 * 4, torch.float32, (L.rows_cap, 16))[:n_sel]
         c = cq.to(torch.float32).sum(dim=0).view(n_sel, 16, 128) * cs.unsqueeze(2)
