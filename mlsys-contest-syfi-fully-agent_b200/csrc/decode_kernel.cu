@@ -379,8 +379,9 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_w1, const __grid_constant__
   __syncthreads();
   tc_fence_after_sync();
   const int tiles = fa->tiles;
-  // a tile has at most n / tiles-of-the-GEMM + 2 pieces; the SwiGLU phase sums up to 8 slabs
-  if (threadIdx.x == 0 && tiles > 0 && static_cast<int>(gridDim.x) / (tiles * kMT1) + 2 > 8) {
+  // a tile has at most n / tiles-of-the-GEMM + 2 pieces; the SwiGLU phase sums up to 8 slabs, the combine 6
+  if (threadIdx.x == 0 && tiles > 0 &&
+      (static_cast<int>(gridDim.x) / (tiles * kMT1) + 2 > 8 || static_cast<int>(gridDim.x) / (tiles * kMT2) + 2 > 6)) {
     atomicOr(&sched->status, kErrSchedOverflow);
   }
   const int n_sel_pad = fa->n_sel_pad;
@@ -582,7 +583,7 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_w1, const __grid_constant__
           const int le = __ffs(rest) - 1;
           return tile_pieces(aux->prefix[le] * kMT2 + m, U2, G2, n_ctas);
         };
-        combine_unit(a.o, slab, slabs, __popc(mask), a.g.tok_rows + t * kTopK, a.g.perm_weight, col,
+        combine_unit<6>(a.o, slab, slabs, __popc(mask), fa->rows[t], fa->permw, col,
                      a.g.out_rows ? a.g.out_rows[t] : a.g.out_bf16 + static_cast<size_t>(t) * kH);
       }
     }

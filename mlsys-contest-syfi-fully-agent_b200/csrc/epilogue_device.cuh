@@ -132,27 +132,42 @@ __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
 }
 
 // Weighted combine of 4 output columns of one token: the token's local experts in ascending
-// order, each the sum of its GEMM2 split-K slabs, multiply then add (the definition's
-// index_add_(O * w), references/moe.py:196-200), bf16 round-to-nearest-even.
-// `slabs(j)` gives the number of slabs of the token's j-th row.
-template <typename SlabCount>
+// order, each the sum of its GEMM2 split-K slabs (in slab order), multiply then add (the definition's
+// index_add_(O * w), references/moe.py:196-200), bf16 round-to-nearest-even.  `slabs(j)` gives the
+// number of slabs (<= kMaxSlabs) of the token's j-th row.  Rows are taken two at a time with all their
+// slab loads in flight: the loads are L2 round trips and would otherwise run one after the other.
+template <int kMaxSlabs, typename SlabCount>
 __device__ __forceinline__ void combine_unit(const float* o, size_t slab, SlabCount slabs, int n_local, const int* rows,
                                              const float* perm_weight, int c, uint16_t* out_row) {
   float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-  for (int j = 0; j < n_local; ++j) {
-    const int row = rows[j];
-    const float w = perm_weight[row];
-    const float* p = o + static_cast<size_t>(row) * kH + c * 4;
-    float4 v = __ldcg(reinterpret_cast<const float4*>(p));
-    const int split = slabs(j);
-    for (int s = 1; s < split; ++s) {
-      const float4 u = __ldcg(reinterpret_cast<const float4*>(p + s * slab));
-      v.x += u.x; v.y += u.y; v.z += u.z; v.w += u.w;
+  for (int j0 = 0; j0 < n_local; j0 += 2) {
+    float4 u[2][kMaxSlabs];
+    float w[2];
+    int ns[2];
+#pragma unroll
+    for (int d = 0; d < 2; ++d) {
+      const bool on = j0 + d < n_local;
+      const int row = on ? rows[j0 + d] : 0;
+      w[d] = on ? perm_weight[row] : 0.0f;
+      ns[d] = on ? slabs(j0 + d) : 0;
+      const float* p = o + static_cast<size_t>(row) * kH + c * 4;
+#pragma unroll
+      for (int s = 0; s < kMaxSlabs; ++s)
+        u[d][s] = s < ns[d] ? __ldcg(reinterpret_cast<const float4*>(p + s * slab)) : make_float4(0.f, 0.f, 0.f, 0.f);
     }
-    acc.x = __fadd_rn(acc.x, __fmul_rn(v.x, w));
-    acc.y = __fadd_rn(acc.y, __fmul_rn(v.y, w));
-    acc.z = __fadd_rn(acc.z, __fmul_rn(v.z, w));
-    acc.w = __fadd_rn(acc.w, __fmul_rn(v.w, w));
+#pragma unroll
+    for (int d = 0; d < 2; ++d) {
+      if (j0 + d < n_local) {
+        float4 v = u[d][0];
+#pragma unroll
+        for (int s = 1; s < kMaxSlabs; ++s)
+          if (s < ns[d]) { v.x += u[d][s].x; v.y += u[d][s].y; v.z += u[d][s].z; v.w += u[d][s].w; }
+        acc.x = __fadd_rn(acc.x, __fmul_rn(v.x, w[d]));
+        acc.y = __fadd_rn(acc.y, __fmul_rn(v.y, w[d]));
+        acc.z = __fadd_rn(acc.z, __fmul_rn(v.z, w[d]));
+        acc.w = __fadd_rn(acc.w, __fmul_rn(v.w, w[d]));
+      }
+    }
   }
   uint2 q;
   q.x = pack_bf16x2(acc.x, acc.y);

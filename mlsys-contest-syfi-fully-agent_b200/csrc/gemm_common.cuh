@@ -44,6 +44,8 @@ struct FusedAux {
   float tw[kFusedMaxTokens][kTopK];   // and its combination weights
   uint32_t mask[kFusedMaxTokens];     // per token: selected local experts
   uint32_t colmask[kELocal];          // per local expert: tokens that selected it
+  int rows[kFusedMaxTokens][kTopK];   // per token: its rows in ascending local expert order
+  float permw[kFusedMaxTokens * kTopK];   // per row: combination weight
   int tiles, n_sel_pad, n_sel;        // active experts (one token tile each), slab stride, rows
 };
 static_assert(sizeof(FusedAux) <= 4096, "FusedAux must fit its slot");
@@ -168,20 +170,18 @@ __device__ __forceinline__ void decode_route_schedule(const GemmArgs& a, uint8_t
       if (lane == 0) gsc[u] = __uint_as_float(u1) + __uint_as_float(u2);
     }
   }
+  if (threadIdx.x == 0) MOE_ROUTE_TRACE(6);
   __syncthreads();
+  if (threadIdx.x == 0) MOE_ROUTE_TRACE(7);
   // Step B for up to two tokens per warp (t and t + kWarps), interleaved: the rounds of a token are a
   // dependent chain of warp reductions, those of two tokens are independent.
   {
     constexpr int kTok = (kFusedMaxTokens + kWarps - 1) / kWarps;   // 2
     uint32_t kq[kTok][kTopKGroup];
     int gq[kTok][kTopKGroup];
-    float sel_s[kTok], sum[kTok];
-    int sel_idx[kTok];
 #pragma unroll
     for (int b = 0; b < kTok; ++b) {
       const int t = warp + b * kWarps;
-      sel_s[b] = sum[b] = 0.0f;
-      sel_idx[b] = 0;
       if (t < a.T) {
         // the four best groups (ties: lower group first), ascending in gq
         const float gs = gsc[t * kNGroup + (lane & 7)];
@@ -213,32 +213,40 @@ __device__ __forceinline__ void decode_route_schedule(const GemmArgs& a, uint8_t
           for (int q = 1; q < kTopKGroup; ++q)
             if (kq[b][q] > best) { best = kq[b][q]; bq = q; }
           const uint32_t m = __reduce_max_sync(0xFFFFFFFFu, best);
-          const uint32_t win = __reduce_min_sync(0xFFFFFFFFu, best == m ? static_cast<uint32_t>(bq * 32 + lane) : 0xFFFFFFFFu);
-          const int wq = win >> 5, wl = win & 31;
-          int wg = gq[b][0];
+          const uint32_t who = __ballot_sync(0xFFFFFFFFu, best == m);
+          int wl = __ffs(who) - 1;
+          if (who & (who - 1)) {   // several lanes hold the maximum (rare): the lowest (group, lane) wins
+            const uint32_t win = __reduce_min_sync(0xFFFFFFFFu, best == m ? static_cast<uint32_t>(bq * 32 + lane) : 0xFFFFFFFFu);
+            wl = (win >> 5) == static_cast<uint32_t>(bq) && (win & 31) == static_cast<uint32_t>(lane) ? lane : -1;
+            wl = __ffs(__ballot_sync(0xFFFFFFFFu, wl == lane)) - 1;
+          }
+          if (lane == wl) {       // the winner records itself; nobody else needs to know before the end
+            int wg = gq[b][0];
 #pragma unroll
-          for (int q = 1; q < kTopKGroup; ++q) wg = (q == wq) ? gq[b][q] : wg;
-          const int idx = wg * 32 + wl;
-          const float sk = sval[t * kEGlobal + idx];
-          sum[b] += sk;                                  // the normaliser is summed in selection order
-          if (lane == r) { sel_s[b] = sk; sel_idx[b] = idx; }
-          if (lane == wl) {
+            for (int q = 1; q < kTopKGroup; ++q) wg = (q == bq) ? gq[b][q] : wg;
+            const int idx = wg * 32 + lane;
+            fa->tidx[t][r] = idx;
+            fa->tw[t][r] = sval[t * kEGlobal + idx];     // unbiased score for now, weight below
 #pragma unroll
-            for (int q = 0; q < kTopKGroup; ++q) kq[b][q] = (q == wq) ? 0u : kq[b][q];   // taken: below every real key
+            for (int q = 0; q < kTopKGroup; ++q) kq[b][q] = (q == bq) ? 0u : kq[b][q];   // taken: below every real key
           }
         }
       }
     }
+    __syncwarp();
 #pragma unroll
     for (int b = 0; b < kTok; ++b) {
       const int t = warp + b * kWarps;
       if (t < a.T) {
-        const float total = sum[b] + 1e-20f;
+        float total = 0.0f;                               // the normaliser is summed in selection order
+#pragma unroll
+        for (int k = 0; k < kTopK; ++k) total += fa->tw[t][k];
+        total += 1e-20f;
+        __syncwarp();
         uint32_t bit = 0;
         if (lane < kTopK) {
-          fa->tidx[t][lane] = sel_idx[b];
-          fa->tw[t][lane] = (sel_s[b] / total) * a.routed_scaling_factor;
-          const int le = sel_idx[b] - a.local_expert_offset;
+          fa->tw[t][lane] = (fa->tw[t][lane] / total) * a.routed_scaling_factor;
+          const int le = fa->tidx[t][lane] - a.local_expert_offset;
           if (le >= 0 && le < kELocal) bit = 1u << le;
         }
         bit = __reduce_or_sync(0xFFFFFFFFu, bit);
@@ -299,14 +307,17 @@ __device__ __forceinline__ void decode_route_schedule(const GemmArgs& a, uint8_t
   }
   if (threadIdx.x == 0) MOE_ROUTE_TRACE(2);
   __syncthreads();
-  if (blockIdx.x == 0 && warp == kFirstEpiWarp && lane < a.T) {   // lane = token: selection, permutation, row lists
+  if (warp == kFirstEpiWarp && lane < a.T) {   // lane = token: row lists and weights (CTA 0 also publishes them)
     const int t = lane;
     const uint32_t m = fa->mask[t];
-    a.local_mask[t] = m;
+    const bool pub = blockIdx.x == 0;
+    if (pub) {
+      a.local_mask[t] = m;
 #pragma unroll
-    for (int k = 0; k < kTopK; ++k) {
-      a.topk_idx[t * kTopK + k] = fa->tidx[t][k];
-      a.topk_w[t * kTopK + k] = fa->tw[t][k];
+      for (int k = 0; k < kTopK; ++k) {
+        a.topk_idx[t * kTopK + k] = fa->tidx[t][k];
+        a.topk_w[t * kTopK + k] = fa->tw[t][k];
+      }
     }
     int j = 0;
     for (uint32_t rest = m; rest; rest &= rest - 1, ++j) {
@@ -316,9 +327,13 @@ __device__ __forceinline__ void decode_route_schedule(const GemmArgs& a, uint8_t
 #pragma unroll
       for (int k = 0; k < kTopK; ++k)
         if (fa->tidx[t][k] - a.local_expert_offset == le) w = fa->tw[t][k];
-      a.perm_token[row] = t;
-      a.perm_weight[row] = w;
-      a.tok_rows[t * kTopK + j] = row;
+      fa->rows[t][j] = row;
+      fa->permw[row] = w;
+      if (pub) {
+        a.perm_token[row] = t;
+        a.perm_weight[row] = w;
+        a.tok_rows[t * kTopK + j] = row;
+      }
     }
   }
 }
