@@ -48,9 +48,9 @@ WORKLOADS = {
     "prefill_t4096": dict(T=4096, token_seed=0, skew=False),
 }
 
-# dram__bytes_read.sum + dram__bytes_write.sum of one GEMM1 launch, from the ncu capture
+# dram__bytes_read.sum + dram__bytes_write.sum of one launch of the dominant kernel, from the ncu capture
 # summarised in profiles/ (None until a capture of that workload exists).
-NCU_TRAFFIC_BYTES = {"decode_t1": 58_828_288 + 54_528,        # profiles/grouped_gemm_fused_decode_t1.md
+NCU_TRAFFIC_BYTES = {"decode_t1": None,                        # set from profiles/decode_kernel_t1.md
                      "skew_t64": 473_900_000 + 12_600_000,     # profiles/launch_shares_skew_t64_prefill_t4096.md
                      "prefill_t4096": 810_400_000 + 69_200_000}
 
@@ -220,14 +220,20 @@ def bench_single(args):
     loader.set_profiling(False)
     stage_us = {k: v / nprof * 1e3 for k, v in acc.items()}
     fused = T <= 16
-    dominant = max(("gemm1", "gemm2"), key=lambda k: stage_us[k])
-    wbytes = W13_BYTES if dominant == "gemm1" else W2_BYTES
-    rbytes = ROW_BYTES if dominant == "gemm1" else 0
-    kernel_bytes = sched.n_active * wbytes + sched.n_sel * rbytes
-    peak, peak_kind = measured_peaks()
-    achieved = kernel_bytes / (stage_us[dominant] * 1e-6) / 1e9
     n_local_tokens = int((im["local_mask"] != 0).sum())
     op_bytes = algorithmic_bytes(T, sched.n_sel, sched.n_active, n_local_tokens)
+    peak, peak_kind = measured_peaks()
+    if fused:
+        # one launch per step: the kernel's average launch duration is the timed region / K
+        dominant, kernel_bytes, launch_us = "decode", op_bytes, ms_step * 1e3
+        kernel_name = "decode_kernel: routing + GEMM1 + SwiGLU + GEMM2 + combine in one launch"
+    else:
+        dominant = max(("gemm1", "gemm2"), key=lambda k: stage_us[k])
+        wbytes = W13_BYTES if dominant == "gemm1" else W2_BYTES
+        rbytes = ROW_BYTES if dominant == "gemm1" else 0
+        kernel_bytes, launch_us = sched.n_active * wbytes + sched.n_sel * rbytes, stage_us[dominant]
+        kernel_name = f"grouped_gemm_kernel<{1 if dominant == 'gemm1' else 2},{sched.n_tile}>"
+    achieved = kernel_bytes / (launch_us * 1e-6) / 1e9
     step(0)       # leave `out` holding replica 0's result for the self-check below
     torch.cuda.synchronize()
 
@@ -264,12 +270,10 @@ def bench_single(args):
         "gpu_launches": int(launches),
         "clocks": clocks.summary(),
         "roofline": {"bound": "hbm",
-                     "kernel": f"grouped_gemm_kernel<{1 if dominant == 'gemm1' else 2},{sched.n_tile}"
-                               + (",fused>: in-kernel routing + GEMM + " + ("SwiGLU" if dominant == "gemm1" else "combine")
-                                  + " tail" if fused else ">"),
+                     "kernel": kernel_name,
                      "achieved": achieved, "peak": peak, "peak_kind": peak_kind, "unit": "GB/s",
                      "frac": achieved / peak, "traffic": NCU_TRAFFIC_BYTES.get(name),
-                     "algorithmic_bytes_per_launch": kernel_bytes, "launch_us": stage_us[dominant],
+                     "algorithmic_bytes_per_launch": kernel_bytes, "launch_us": launch_us,
                      "whole_op": {"algorithmic_bytes": op_bytes, "achieved": op_bytes / (ms_step * 1e-3) / 1e9,
                                   "frac": op_bytes / (ms_step * 1e-3) / 1e9 / peak}},
         "stage_us": stage_us,
@@ -315,8 +319,9 @@ def sweep(pkg, W, names, peak):
         us = ms * 1e3
         rows.append({"workload": name, "T": T, "n_sel": s.n_sel, "active_experts": s.n_active, "replicas": R,
                      "us_per_step": us, "tokens_per_s": T / us * 1e6,
-                     "gemm1_gbs": (s.n_active * W13_BYTES + s.n_sel * ROW_BYTES) / acc["gemm1"] / 1e3,
-                     "gemm2_gbs": s.n_active * W2_BYTES / acc["gemm2"] / 1e3,
+                     # T <= 16 is one launch: no per-GEMM split
+                     "gemm1_gbs": None if T <= 16 else (s.n_active * W13_BYTES + s.n_sel * ROW_BYTES) / acc["gemm1"] / 1e3,
+                     "gemm2_gbs": None if T <= 16 else s.n_active * W2_BYTES / acc["gemm2"] / 1e3,
                      "whole_op_hbm_frac": s.n_active * (W13_BYTES + W2_BYTES) / us / 1e3 / peak,
                      "fp8_tflops": s.n_sel * 88080384 / us / 1e6,
                      "stage_us": acc})

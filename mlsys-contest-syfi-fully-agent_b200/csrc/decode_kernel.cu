@@ -36,6 +36,7 @@
 namespace moe { __device__ unsigned long long g_moe_dtrace[148][4][16]; }
 #define DTRACE(role, slot) do { if (blockIdx.x < 148) moe::g_moe_dtrace[blockIdx.x][role][slot] = moe::globaltimer_ns(); } while (0)
 #define MOE_ROUTE_TRACE(slot) DTRACE(3, slot)
+#define MOE_ROUTE_CLK(slot) do { if (blockIdx.x < 148) moe::g_moe_dtrace[blockIdx.x][0][slot] = clock64(); } while (0)
 #else
 #define DTRACE(role, slot) do { } while (0)
 #endif

@@ -5,6 +5,9 @@
 #include "ptx.cuh"
 #include "route_device.cuh"
 
+#ifndef MOE_ROUTE_CLK
+#define MOE_ROUTE_CLK(slot) do { } while (0)
+#endif
 #ifndef MOE_ROUTE_TRACE
 #define MOE_ROUTE_TRACE(slot) do { } while (0)   // debug builds of an including file may stamp the routing phases
 #endif
@@ -131,128 +134,146 @@ __device__ __forceinline__ void decode_route_schedule(const GemmArgs& a, uint8_t
                                                       MoeSched* sched) {
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  // Routing in two steps (same arithmetic and tie rules as route_token; the work is spread over all warps and
-  // the instruction count per token is a third).  Step A, one warp per (token, routing group), lane = expert:
-  // sigmoid + bias -> key (kept in shared memory with the unbiased score), two rounds of warp arg-max for the
-  // group score.  Step B, one warp per token: the four best groups, then every lane holds its expert of each
-  // kept group and eight rounds of arg-max over the 128 candidates give the selection in descending order.
-  uint32_t* skey = reinterpret_cast<uint32_t*>(smem);             // [T][256] keys; the stage ring is still idle
-  float* sval = reinterpret_cast<float*>(smem) + kFusedMaxTokens * kEGlobal;      // [T][256] unbiased scores
-  float* gsc = reinterpret_cast<float*>(smem) + 2 * kFusedMaxTokens * kEGlobal;   // [T][8]   group scores
+  // Routing, one warp per token (same arithmetic and tie rules as route_token), organised around what is cheap
+  // on this machine: shuffles and plain comparisons are, reduce / vote chains are not (a round of warp arg-max
+  // costs ~300 cycles of latency).  Measured: ~2.5 us for one token, ~5.5 us for sixteen (two per warp).
+  // Lane l holds the 8 consecutive experts 8l .. 8l+7, so a routing group is 4 adjacent lanes:
+  //   * sigmoid + bias -> order-preserving keys; the lane's two best by plain comparisons; two xor-shuffle
+  //     steps merge them over the group's 4 lanes -> group score (sum of its two best biased scores);
+  //   * the four best groups by comparing against the 8 scores (8 shuffles);
+  //   * candidates are 64-bit words {key, 255 - expert}: a larger word is a better candidate, ties on the key
+  //     go to the lower expert; lanes of dropped groups hold zeros.  Every lane sorts its 8 words (19-exchange
+  //     network), then five butterfly steps merge the lists: with the partner's list reversed, the element-wise
+  //     maximum is the top 8 of both lists as a bitonic sequence, which a 3-stage merge network sorts.  After
+  //     the last step every lane holds the selection in descending order.
   float* bias_s = fa->sval;
   for (int i = threadIdx.x; i < kEGlobal; i += kGemmThreads)
     bias_s[i] = __uint_as_float(static_cast<uint32_t>(a.bias_bf16[i]) << 16);
+  float* sval = reinterpret_cast<float*>(smem);                   // [T][256] unbiased scores; the stage ring is still idle
   constexpr int kWarps = kGemmThreads / 32;
-  constexpr int kMaxUnits = (kFusedMaxTokens * kNGroup + kWarps - 1) / kWarps;
-  const int units = a.T * kNGroup;
-  float x[kMaxUnits];
+  constexpr int kTok = (kFusedMaxTokens + kWarps - 1) / kWarps;   // tokens per warp: t = warp, warp + kWarps
+  static_assert(kTok == 2, "two tokens per warp at most");
+  float4 xa[kTok], xb[kTok];
 #pragma unroll
-  for (int i = 0; i < kMaxUnits; ++i) {                            // all logits of this warp's units in flight
-    const int u = warp + i * kWarps;
-    x[i] = u < units ? a.logits[static_cast<size_t>(u) * 32 + lane] : 0.0f;      // [t][g][lane] = [u][lane]
+  for (int b = 0; b < kTok; ++b) {                                 // both tokens' logits in flight
+    const int t = warp + b * kWarps;
+    xa[b] = xb[b] = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (t < a.T) {
+      const float4* row = reinterpret_cast<const float4*>(a.logits + static_cast<size_t>(t) * kEGlobal + lane * 8);
+      xa[b] = row[0];
+      xb[b] = row[1];
+    }
   }
   __syncthreads();
   if (threadIdx.x == 0) MOE_ROUTE_TRACE(0);
-#pragma unroll
-  for (int i = 0; i < kMaxUnits; ++i) {
-    const int u = warp + i * kWarps;
-    if (u < units) {                                               // uniform over the warp
-      const float s = 1.0f / (1.0f + expf(-x[i]));
-      const uint32_t key = order_key(s + bias_s[(u & 7) * 32 + lane]);
-      skey[u * 32 + lane] = key;
-      sval[u * 32 + lane] = s;
-      // group score = best + second best biased score (ties: any; undo the order-preserving map)
-      const uint32_t k1 = __reduce_max_sync(0xFFFFFFFFu, key);
-      const int first = __ffs(__ballot_sync(0xFFFFFFFFu, key == k1)) - 1;
-      const uint32_t k2 = __reduce_max_sync(0xFFFFFFFFu, lane == first ? 0u : key);
-      const uint32_t u1 = (k1 & 0x80000000u) ? (k1 & 0x7FFFFFFFu) : ~k1;
-      const uint32_t u2 = (k2 & 0x80000000u) ? (k2 & 0x7FFFFFFFu) : ~k2;
-      if (lane == 0) gsc[u] = __uint_as_float(u1) + __uint_as_float(u2);
-    }
-  }
-  if (threadIdx.x == 0) MOE_ROUTE_TRACE(6);
-  __syncthreads();
-  if (threadIdx.x == 0) MOE_ROUTE_TRACE(7);
-  // Step B for up to two tokens per warp (t and t + kWarps), interleaved: the rounds of a token are a
-  // dependent chain of warp reductions, those of two tokens are independent.
-  {
-    constexpr int kTok = (kFusedMaxTokens + kWarps - 1) / kWarps;   // 2
-    uint32_t kq[kTok][kTopKGroup];
-    int gq[kTok][kTopKGroup];
+  // Both tokens of a warp go through every step together (b = 0, 1): the steps of one token are a chain of
+  // dependent operations, those of two tokens are independent and overlap.  `on[b]` is uniform over the warp.
+  if (warp < a.T) {
+    const bool on[kTok] = {true, warp + kWarps < a.T};
+    unsigned long long c[kTok][8];
+    if (threadIdx.x == 0) MOE_ROUTE_CLK(8);
 #pragma unroll
     for (int b = 0; b < kTok; ++b) {
+      if (!on[b]) continue;
       const int t = warp + b * kWarps;
-      if (t < a.T) {
-        // the four best groups (ties: lower group first), ascending in gq
-        const float gs = gsc[t * kNGroup + (lane & 7)];
-        int grank = 0;
+      const float4 va = xa[b], vb = xb[b];
+      const float x[8] = {va.x, va.y, va.z, va.w, vb.x, vb.y, vb.z, vb.w};
+      float s[8];
+      uint32_t k[8];
+      uint32_t m1 = 0u, m2 = 0u;                                   // the lane's two best keys (m1 >= m2)
 #pragma unroll
-        for (int h = 0; h < kNGroup; ++h) {
-          const float gh = __shfl_sync(0xFFFFFFFFu, gs, h);
-          grank += (gh > gs) || (gh == gs && h < (lane & 7));
-        }
-        uint32_t keep = __ballot_sync(0xFFFFFFFFu, lane < kNGroup && grank < kTopKGroup);
-#pragma unroll
-        for (int q = 0; q < kTopKGroup; ++q) {
-          gq[b][q] = __ffs(keep) - 1;
-          keep &= keep - 1;
-          kq[b][q] = skey[t * kEGlobal + gq[b][q] * 32 + lane];
-        }
+      for (int i = 0; i < 8; ++i) {
+        s[i] = 1.0f / (1.0f + expf(-x[i]));
+        k[i] = order_key(s[i] + bias_s[lane * 8 + i]);
+        if (k[i] > m1) { m2 = m1; m1 = k[i]; }
+        else if (k[i] > m2) m2 = k[i];
       }
+      float4* sv = reinterpret_cast<float4*>(sval + t * kEGlobal + lane * 8);
+      sv[0] = make_float4(s[0], s[1], s[2], s[3]);
+      sv[1] = make_float4(s[4], s[5], s[6], s[7]);
+#pragma unroll
+      for (int d = 1; d <= 2; d <<= 1) {                           // merge over the group's 4 lanes
+        const uint32_t o1 = __shfl_xor_sync(0xFFFFFFFFu, m1, d), o2 = __shfl_xor_sync(0xFFFFFFFFu, m2, d);
+        const uint32_t n2 = m1 >= o1 ? max(m2, o1) : max(o2, m1);
+        m1 = max(m1, o1);
+        m2 = n2;
+      }
+      const float gs = __uint_as_float((m1 & 0x80000000u) ? (m1 & 0x7FFFFFFFu) : ~m1) +
+                       __uint_as_float((m2 & 0x80000000u) ? (m2 & 0x7FFFFFFFu) : ~m2);
+      const int g = lane >> 2;
+      int grank = 0;                                               // ties: lower group first
+#pragma unroll
+      for (int h = 0; h < kNGroup; ++h) {
+        const float gh = __shfl_sync(0xFFFFFFFFu, gs, h * 4);
+        grank += (gh > gs) || (gh == gs && h < g);
+      }
+      const bool kept = grank < kTopKGroup;
+#pragma unroll
+      for (int i = 0; i < 8; ++i)
+        c[b][i] = kept ? (static_cast<unsigned long long>(k[i]) << 32) | static_cast<unsigned int>(255 - (lane * 8 + i)) : 0ull;
+    }
+    if (threadIdx.x == 0) MOE_ROUTE_CLK(9);
+#define MOE_CX(p, q)                                               \
+    {                                                              \
+      const unsigned long long hi = max(c[b][p], c[b][q]);         \
+      c[b][q] = min(c[b][p], c[b][q]);                             \
+      c[b][p] = hi;                                                \
     }
 #pragma unroll
-    for (int r = 0; r < kTopK; ++r) {
+    for (int b = 0; b < kTok; ++b) {                               // the lane's own list, descending
+      if (!on[b]) continue;
+      MOE_CX(0, 1) MOE_CX(2, 3) MOE_CX(4, 5) MOE_CX(6, 7)
+      MOE_CX(0, 2) MOE_CX(1, 3) MOE_CX(4, 6) MOE_CX(5, 7)
+      MOE_CX(1, 2) MOE_CX(5, 6) MOE_CX(0, 4) MOE_CX(3, 7)
+      MOE_CX(1, 5) MOE_CX(2, 6)
+      MOE_CX(1, 4) MOE_CX(3, 6)
+      MOE_CX(2, 4) MOE_CX(3, 5)
+      MOE_CX(3, 4)
+    }
+    if (threadIdx.x == 0) MOE_ROUTE_CLK(10);
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) {                             // butterfly merge over the warp
 #pragma unroll
       for (int b = 0; b < kTok; ++b) {
-        const int t = warp + b * kWarps;
-        if (t < a.T) {
-          // this lane's best candidate (ties: lower group), then the warp's (ties: lower expert index)
-          uint32_t best = kq[b][0];
-          int bq = 0;
+        if (!on[b]) continue;
+        unsigned long long o[8];
 #pragma unroll
-          for (int q = 1; q < kTopKGroup; ++q)
-            if (kq[b][q] > best) { best = kq[b][q]; bq = q; }
-          const uint32_t m = __reduce_max_sync(0xFFFFFFFFu, best);
-          const uint32_t who = __ballot_sync(0xFFFFFFFFu, best == m);
-          int wl = __ffs(who) - 1;
-          if (who & (who - 1)) {   // several lanes hold the maximum (rare): the lowest (group, lane) wins
-            const uint32_t win = __reduce_min_sync(0xFFFFFFFFu, best == m ? static_cast<uint32_t>(bq * 32 + lane) : 0xFFFFFFFFu);
-            wl = (win >> 5) == static_cast<uint32_t>(bq) && (win & 31) == static_cast<uint32_t>(lane) ? lane : -1;
-            wl = __ffs(__ballot_sync(0xFFFFFFFFu, wl == lane)) - 1;
-          }
-          if (lane == wl) {       // the winner records itself; nobody else needs to know before the end
-            int wg = gq[b][0];
+        for (int i = 0; i < 8; ++i) o[i] = __shfl_xor_sync(0xFFFFFFFFu, c[b][7 - i], d);
 #pragma unroll
-            for (int q = 1; q < kTopKGroup; ++q) wg = (q == bq) ? gq[b][q] : wg;
-            const int idx = wg * 32 + lane;
-            fa->tidx[t][r] = idx;
-            fa->tw[t][r] = sval[t * kEGlobal + idx];     // unbiased score for now, weight below
-#pragma unroll
-            for (int q = 0; q < kTopKGroup; ++q) kq[b][q] = (q == bq) ? 0u : kq[b][q];   // taken: below every real key
-          }
-        }
+        for (int i = 0; i < 8; ++i) c[b][i] = max(c[b][i], o[i]);
+        MOE_CX(0, 4) MOE_CX(1, 5) MOE_CX(2, 6) MOE_CX(3, 7)
+        MOE_CX(0, 2) MOE_CX(1, 3) MOE_CX(4, 6) MOE_CX(5, 7)
+        MOE_CX(0, 1) MOE_CX(2, 3) MOE_CX(4, 5) MOE_CX(6, 7)
       }
     }
-    __syncwarp();
+#undef MOE_CX
+    if (threadIdx.x == 0) MOE_ROUTE_CLK(11);
+    __syncwarp();                                                  // the warp's unbiased scores are in shared memory
 #pragma unroll
     for (int b = 0; b < kTok; ++b) {
+      if (!on[b]) continue;
       const int t = warp + b * kWarps;
-      if (t < a.T) {
-        float total = 0.0f;                               // the normaliser is summed in selection order
+      float total = 0.0f, mine = 0.0f;                             // the normaliser is summed in selection order
+      int my_idx = 0;
 #pragma unroll
-        for (int k = 0; k < kTopK; ++k) total += fa->tw[t][k];
-        total += 1e-20f;
-        __syncwarp();
-        uint32_t bit = 0;
-        if (lane < kTopK) {
-          fa->tw[t][lane] = (fa->tw[t][lane] / total) * a.routed_scaling_factor;
-          const int le = fa->tidx[t][lane] - a.local_expert_offset;
-          if (le >= 0 && le < kELocal) bit = 1u << le;
-        }
-        bit = __reduce_or_sync(0xFFFFFFFFu, bit);
-        if (lane == 0) fa->mask[t] = bit;
+      for (int q = 0; q < kTopK; ++q) {
+        const int idx = 255 - static_cast<int>(static_cast<unsigned int>(c[b][q]) & 0xFFu);
+        const float sq = sval[t * kEGlobal + idx];
+        total += sq;
+        if (lane == q) { mine = sq; my_idx = idx; }
       }
+      total += 1e-20f;
+      uint32_t bit = 0;
+      if (lane < kTopK) {
+        fa->tidx[t][lane] = my_idx;
+        fa->tw[t][lane] = (mine / total) * a.routed_scaling_factor;
+        const int le = my_idx - a.local_expert_offset;
+        if (le >= 0 && le < kELocal) bit = 1u << le;
+      }
+      bit = __reduce_or_sync(0xFFFFFFFFu, bit);
+      if (lane == 0) fa->mask[t] = bit;
     }
+    if (threadIdx.x == 0) MOE_ROUTE_CLK(12);
   }
   if (threadIdx.x == 0) MOE_ROUTE_TRACE(1);
   fence_proxy_async_smem();   // the logits scratch is about to be overwritten by TMA (async proxy)
