@@ -116,7 +116,11 @@ LIVE_CASES = [
     (1, 0, False, 0),        # no local expert at all: all-zero output
     (2, 5, False, 32),
     (3, 7, False, 224),      # last shard
+    (5, 11, True, 0),        # decode kernel, several tokens per expert
+    (9, 14, False, 128),
+    (13, 12, False, 0),      # more tokens than routing warps in the decode kernel
     (16, 1, False, 0),
+    (16, 13, True, 0),       # decode kernel at its largest: 128 rows on 8 experts
     (17, 2, False, 96),
     (33, 4, True, 0),        # every token lands on 8 local experts
     (127, 6, False, 0),
