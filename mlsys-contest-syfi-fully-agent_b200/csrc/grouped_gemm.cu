@@ -43,8 +43,11 @@ namespace moe {
 // Debug build only: per-role time stamps of CTA 0, [gemm][role][slot].
 __device__ unsigned long long g_moe_trace[2][4][256];
 #define TRACE(role, slot) do { if (blockIdx.x == 0 && (slot) < 256) g_moe_trace[GEMM - 1][role][slot] = static_cast<unsigned long long>(clock64()); } while (0)
+// per-stage stamps of CTA 0 in steady state: stages 40..71 of the CTA, `per` stamps each
+#define TRACE_STAGE(role, n, per, j) do { if ((n) >= 40 && (n) < 72) TRACE(role, ((n) - 40) * (per) + (j)); } while (0)
 #else
 #define TRACE(role, slot) do { } while (0)
+#define TRACE_STAGE(role, n, per, j) do { } while (0)
 #endif
 
 namespace {
@@ -187,12 +190,15 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
       const uint32_t full_base = smem_u32(&aux->full[0]), done_base = smem_u32(&aux->done[0]);
       uint32_t stage = 0, ph = 0;
       bool ok = true;
+      [[maybe_unused]] int nst = 0;
       for (int i = blockIdx.x; ok && i < items; i += gridDim.x) {
         const Item w = decode_item<GEMM, N_TILE>(i, split, aux);
         const int wy = w.e * C::M_TOTAL + w.m * 128;
         const int by = w.row0;
-        for (int kb = w.kb0; kb < w.kb1; kb += C::KPS) {
+        for (int kb = w.kb0; kb < w.kb1; kb += C::KPS, ++nst) {
+          TRACE_STAGE(0, nst, 2, 0);
           if (!mbar_wait(done_base + stage * 8, ph ^ 1u, abort_flag)) { ok = false; break; }
+          TRACE_STAGE(0, nst, 2, 1);
           const uint32_t bar = full_base + stage * 8;
           mbar_arrive_expect_tx(bar, C::STAGE_BYTES);
           const uint32_t dst = smem_base + stage * C::STAGE_BYTES;
@@ -218,11 +224,15 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
       const uint32_t tempty_base = smem_u32(&aux->tempty[0]);
       uint32_t stage = 0, ph = 0, buf = 0, bph = 0;
       bool ok = true;
+      [[maybe_unused]] int nst = 0;
       for (int i = blockIdx.x; ok && i < items; i += gridDim.x) {
         const Item w = decode_item<GEMM, N_TILE>(i, split, aux);
-        for (int kb = w.kb0; kb < w.kb1; kb += C::KPS) {        // items span whole stages
+        for (int kb = w.kb0; kb < w.kb1; kb += C::KPS, ++nst) {        // items span whole stages
+          TRACE_STAGE(1, nst, 4, 0);
           if (!mbar_wait(tempty_base + buf * 8, bph ^ 1u, abort_flag)) { ok = false; break; }
+          TRACE_STAGE(1, nst, 4, 1);
           if (!mbar_wait(full_base + stage * 8, ph, abort_flag)) { ok = false; break; }
+          TRACE_STAGE(1, nst, 4, 2);
           tc_fence_after_sync();
           const uint32_t sbase = smem_base + stage * C::STAGE_BYTES;
 #pragma unroll
@@ -239,6 +249,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
             }
           }
           umma_commit(done_base + stage * 8);
+          TRACE_STAGE(1, nst, 4, 3);
           if (++stage == C::STAGES) { stage = 0; ph ^= 1u; }
           if (++buf == C::NBUF) { buf = 0; bph ^= 1u; }
         }
@@ -254,6 +265,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
     const int etid = threadIdx.x - kFirstEpiWarp * 32;   // 0..255
     const uint32_t lane_addr = static_cast<uint32_t>(q * 32) << 16;
     uint32_t eph = 0, nitem = 0;
+    [[maybe_unused]] int nst = 0;
     uint32_t stage = 0, ph = 0, buf = 0, bph = 0;      // same ring positions as the issuer
     const uint32_t done_base = smem_u32(&aux->done[0]), tempty_base = smem_u32(&aux->tempty[0]);
     bool ok = true;
@@ -288,7 +300,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
     for (int i = blockIdx.x; ok && i < items; i += gridDim.x, ++nitem) {
       const Item w = decode_item<GEMM, N_TILE>(i, split, aux);
       const int nkb = w.kb1 - w.kb0;
-      if (etid == 0) TRACE(2, 128 + 2 * nitem);
+      if (etid == 0 && nitem < 16) TRACE(3, 32 + 4 * nitem);
       float* sc = sc_base + (C::SC_BUFS == 2 ? (nitem & 1u) * (C::KB * N_TILE) : 0);
       const int inext = i + gridDim.x;
       if (C::SC_BUFS == 1) {
@@ -303,14 +315,16 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
 #pragma unroll
         for (int x = 0; x < kMaxE; ++x) pre[x] = load_scale(wn, etid + x * kEpiThreads);
       }
-      if (etid == 0) TRACE(2, 128 + 2 * nitem + 1);
+      if (etid == 0 && nitem < 16) TRACE(3, 33 + 4 * nitem);
 
       float acc[C::CPW];
 #pragma unroll
       for (int j = 0; j < C::CPW; ++j) acc[j] = 0.0f;
 
-      for (int kbl = 0; kbl < nkb; kbl += C::G) {
+      for (int kbl = 0; kbl < nkb; kbl += C::G, ++nst) {
+        if (etid == 0) TRACE_STAGE(2, nst, 4, 0);
         if (!mbar_wait(done_base + stage * 8, ph, abort_flag)) { ok = false; break; }
+        if (etid == 0) TRACE_STAGE(2, nst, 4, 1);
         tc_fence_after_sync();
         const uint32_t taddr = tmem_base + lane_addr + buf * (C::G * C::KB_COLS) + h * C::CPW;
 #pragma unroll
@@ -327,6 +341,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
               tc_fence_before_sync();
               __syncwarp();
               if (lane == 0) mbar_arrive(tempty_base + buf * 8);
+              if (etid == 0) TRACE_STAGE(2, nst, 4, 2);
             }
             const float4* scv = reinterpret_cast<const float4*>(sc + (kbl + g) * N_TILE + h * C::CPW + c0);
 #pragma unroll
@@ -347,10 +362,12 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
             }
           }
         }
+        if (etid == 0) TRACE_STAGE(2, nst, 4, 3);
         if (++stage == C::STAGES) { stage = 0; ph ^= 1u; }
         if (++buf == C::NBUF) { buf = 0; bph ^= 1u; }
       }
       if (!ok) break;
+      if (etid == 0 && nitem < 16) TRACE(3, 34 + 4 * nitem);
       float* out = a.out + (static_cast<size_t>(w.s) * n_sel_pad + w.row0 + h * C::CPW) * C::M_TOTAL + w.m * 128 +
                    q * 32 + lane;
 #pragma unroll
