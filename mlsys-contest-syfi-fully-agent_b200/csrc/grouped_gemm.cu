@@ -65,6 +65,10 @@ struct Cfg {
   static constexpr int MMA_PER_K4 = STACK ? 1 : NTERMS;
   static constexpr int PLANES = STACK ? NTERMS : 1;                     // column planes the epilogue sums
   static constexpr int KB_COLS = N_MMA;                                 // TMEM columns of one K-block partial
+  // 128-token tiles run un-swapped: tokens are the UMMA M operand (TMEM lanes), weight rows the N operand
+  // (TMEM columns).  A promotion thread then owns one token row, so the scale product of a K-block is ONE
+  // value per thread instead of one per token column, and the result row is contiguous in memory.
+  static constexpr bool TOK_ON_M = N_TILE == 128 && GEMM == 1;   // (GEMM2 measured slower un-swapped: its row stores scatter)
   static constexpr int A_BYTES = 128 * 128;
   static constexpr int B_BYTES = N_TILE * 128;
   static constexpr int KB_BYTES = A_BYTES + NTERMS * B_BYTES;           // operands of one K-block
@@ -94,7 +98,7 @@ struct Cfg {
   static constexpr int TMEM_USED = NBUF * G * KB_COLS;
   static constexpr int TMEM_COLS = TMEM_USED <= 32 ? 32 : TMEM_USED <= 64 ? 64 : TMEM_USED <= 128 ? 128
                                    : TMEM_USED <= 256 ? 256 : 512;
-  static_assert(STAGES >= 2, "ring too small");
+  static_assert(STAGES >= 2 && CH <= CPW, "ring too small / read-back chunks");
   static_assert(KB % KPS == 0 && (KPS & (KPS - 1)) == 0, "K-blocks per stage: a power of two dividing the K extent");
   static_assert(NBUF >= 2 && NBUF <= STAGES && TMEM_USED <= 512, "TMEM budget / ring depths");
   static_assert(N_MMA % 16 == 0 && N_MMA >= 16 && N_MMA <= 256, "invalid UMMA N for M = 128");
@@ -244,8 +248,10 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
             for (int t = 0; t < C::MMA_PER_K4; ++t) {
               const uint64_t bdesc = desc_const | ((sb + t * C::B_BYTES) >> 4);
 #pragma unroll
-              for (int k4 = 0; k4 < 4; ++k4)   // +32 bytes of K inside the 128-byte swizzle atom = +2 encoded units
-                umma_f8(d, adesc + 2 * k4, bdesc + 2 * k4, idesc, (t | k4) != 0 ? 1u : 0u);
+              for (int k4 = 0; k4 < 4; ++k4) {  // +32 bytes of K inside the 128-byte swizzle atom = +2 encoded units
+                if constexpr (C::TOK_ON_M) umma_f8(d, bdesc + 2 * k4, adesc + 2 * k4, idesc, (t | k4) != 0 ? 1u : 0u);
+                else umma_f8(d, adesc + 2 * k4, bdesc + 2 * k4, idesc, (t | k4) != 0 ? 1u : 0u);
+              }
             }
           }
           umma_commit(done_base + stage * 8);
@@ -281,14 +287,19 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
     constexpr int kEpiThreads = kEpiWarps * 32;
     constexpr int kMaxE = (C::KB * N_TILE + kEpiThreads - 1) / kEpiThreads;
     auto load_scale = [&](const Item& w, int idx) -> float {
+      // branch-free (clamped addresses, result selected afterwards) so that a thread's loads can all be in flight
       const int nkb = w.kb1 - w.kb0;
-      if (idx >= nkb * N_TILE) return 0.0f;
-      const int kbl = idx / N_TILE, j = idx % N_TILE, kb = w.kb0 + kbl;
+      const bool in = idx < nkb * N_TILE;
+      const int kbl = in ? idx / N_TILE : 0, j = idx % N_TILE, kb = w.kb0 + kbl;
+      const bool valid = in && j < w.valid;
       const float ws = __ldg(a.w_scale + (static_cast<size_t>(w.e) * C::MT + w.m) * C::KB + kb);
-      if (j >= w.valid) return 0.0f;
-      return ws * __ldg(a.b_scale + static_cast<size_t>(w.row0 + j) * C::KB + kb);
+      const float bs = __ldg(a.b_scale + static_cast<size_t>(w.row0 + (valid ? j : 0)) * C::KB + kb);
+      return valid ? ws * bs : 0.0f;
     };
-    float pre[C::SC_BUFS == 2 ? kMaxE : 1];
+    // One table, next item's values prefetched into registers (un-swapped path: its promotion keeps no
+    // per-column scale temporaries, so there is room for them during the K loop)
+    constexpr bool kPrefetch1 = C::SC_BUFS == 1 && C::TOK_ON_M;
+    float pre[(C::SC_BUFS == 2 || kPrefetch1) ? kMaxE : 1];
     if (C::SC_BUFS == 2 && static_cast<int>(blockIdx.x) < items) {
       const Item w0 = decode_item<GEMM, N_TILE>(blockIdx.x, split, aux);
 #pragma unroll
@@ -306,11 +317,19 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
       if (C::SC_BUFS == 1) {
         epi_sync();   // the previous item's scale products are no longer being read
         if (!ok) break;
-        for (int idx = etid; idx < nkb * N_TILE; idx += kEpiThreads) sc[idx] = load_scale(w, idx);
+        if (kPrefetch1 && nitem > 0) {
+#pragma unroll
+          for (int x = 0; x < kMaxE; ++x) {
+            const int idx = etid + x * kEpiThreads;
+            if (idx < nkb * N_TILE) sc[idx] = pre[x];
+          }
+        } else {
+          for (int idx = etid; idx < nkb * N_TILE; idx += kEpiThreads) sc[idx] = load_scale(w, idx);
+        }
       }
       epi_sync();     // this item's table is complete (and, with two tables, the other one is free)
       if (!ok) break;
-      if (C::SC_BUFS == 2 && inext < items) {
+      if ((C::SC_BUFS == 2 || kPrefetch1) && inext < items) {
         const Item wn = decode_item<GEMM, N_TILE>(inext, split, aux);
 #pragma unroll
         for (int x = 0; x < kMaxE; ++x) pre[x] = load_scale(wn, etid + x * kEpiThreads);
@@ -321,6 +340,37 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
 #pragma unroll
       for (int j = 0; j < C::CPW; ++j) acc[j] = 0.0f;
 
+      if constexpr (C::TOK_ON_M) {
+        static_assert(C::PLANES == 1 && C::CPW == 64 && C::KB_COLS == 128, "un-swapped path: one 128 x 128 partial per K-block");
+        // lane = token row (row0 + 32 q + lane), columns = this warp's half of the 128 weight rows
+        const int trow = q * 32 + lane;
+        for (int kbl = 0; kbl < nkb; kbl += C::G, ++nst) {
+          if (etid == 0) TRACE_STAGE(2, nst, 4, 0);
+          if (!mbar_wait(done_base + stage * 8, ph, abort_flag)) { ok = false; break; }
+          if (etid == 0) TRACE_STAGE(2, nst, 4, 1);
+          tc_fence_after_sync();
+          const uint32_t taddr = tmem_base + lane_addr + buf * (C::G * C::KB_COLS) + h * C::CPW;
+#pragma unroll
+          for (int g = 0; g < C::G; ++g) {
+            float v[C::CPW];
+            tmem_ld32(taddr + g * C::KB_COLS, v);
+            tmem_ld32(taddr + g * C::KB_COLS + 32, v + 32);
+            const float f = sc[(kbl + g) * N_TILE + trow];      // w_scale * b_scale of this token row and K-block
+            tmem_wait_ld();
+            if (g == C::G - 1) {
+              tc_fence_before_sync();
+              __syncwarp();
+              if (lane == 0) mbar_arrive(tempty_base + buf * 8);
+              if (etid == 0) TRACE_STAGE(2, nst, 4, 2);
+            }
+#pragma unroll
+            for (int j = 0; j < C::CPW; ++j) acc[j] = fmaf(v[j], f, acc[j]);
+          }
+          if (etid == 0) TRACE_STAGE(2, nst, 4, 3);
+          if (++stage == C::STAGES) { stage = 0; ph ^= 1u; }
+          if (++buf == C::NBUF) { buf = 0; bph ^= 1u; }
+        }
+      } else
       for (int kbl = 0; kbl < nkb; kbl += C::G, ++nst) {
         if (etid == 0) TRACE_STAGE(2, nst, 4, 0);
         if (!mbar_wait(done_base + stage * 8, ph, abort_flag)) { ok = false; break; }
@@ -368,11 +418,20 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
       }
       if (!ok) break;
       if (etid == 0 && nitem < 16) TRACE(3, 34 + 4 * nitem);
-      float* out = a.out + (static_cast<size_t>(w.s) * n_sel_pad + w.row0 + h * C::CPW) * C::M_TOTAL + w.m * 128 +
-                   q * 32 + lane;
+      if constexpr (C::TOK_ON_M) {
+        if (q * 32 + lane < w.valid) {      // one token row, 64 consecutive outputs
+          float4* out = reinterpret_cast<float4*>(a.out + (static_cast<size_t>(w.s) * n_sel_pad + w.row0 + q * 32 + lane) * C::M_TOTAL +
+                                                  w.m * 128 + h * C::CPW);
 #pragma unroll
-      for (int j = 0; j < C::CPW; ++j)
-        if (h * C::CPW + j < w.valid) out[static_cast<size_t>(j) * C::M_TOTAL] = acc[j];
+          for (int j = 0; j < C::CPW / 4; ++j) out[j] = make_float4(acc[4 * j], acc[4 * j + 1], acc[4 * j + 2], acc[4 * j + 3]);
+        }
+      } else {
+        float* out = a.out + (static_cast<size_t>(w.s) * n_sel_pad + w.row0 + h * C::CPW) * C::M_TOTAL + w.m * 128 +
+                     q * 32 + lane;
+#pragma unroll
+        for (int j = 0; j < C::CPW; ++j)
+          if (h * C::CPW + j < w.valid) out[static_cast<size_t>(j) * C::M_TOTAL] = acc[j];
+      }
       if (C::SC_BUFS == 2 && inext < items) {
         float* scn = sc_base + ((nitem + 1) & 1u) * (C::KB * N_TILE);
 #pragma unroll
