@@ -51,8 +51,8 @@ WORKLOADS = {
 # dram__bytes_read.sum + dram__bytes_write.sum of one launch of the dominant kernel, from the ncu capture
 # summarised in profiles/ (None until a capture of that workload exists).
 NCU_TRAFFIC_BYTES = {"decode_t1": 88_237_568 + 2_996_224,     # profiles/decode_kernel_t1.md
-                     "skew_t64": 473_900_000 + 12_600_000,     # profiles/launch_shares_skew_t64_prefill_t4096.md
-                     "prefill_t4096": 810_400_000 + 69_200_000}
+                     "skew_t64": 473_900_000 + 12_800_000,     # profiles/launch_shares_skew_t64_prefill_t4096.md
+                     "prefill_t4096": 807_600_000 + 67_100_000}
 
 W13_BYTES = 4096 * 7168 + 32 * 56 * 4          # one expert's GEMM1 weights + scales
 W2_BYTES = 7168 * 2048 + 56 * 16 * 4
