@@ -68,6 +68,11 @@ struct Cfg {
   // 128-token tiles run un-swapped: tokens are the UMMA M operand (TMEM lanes), weight rows the N operand
   // (TMEM columns).  A promotion thread then owns one token row, so the scale product of a K-block is ONE
   // value per thread instead of one per token column, and the result row is contiguous in memory.
+  // UMMA issuer threads (warps 1 and 2 of the control warpgroup), taking alternate stages.  A stage's UMMAs only
+  // touch that stage's shared memory and TMEM columns and each thread commits its own, so stages are independent;
+  // with one thread the waits and loop overhead between two stages (~500 cycles) leave the tensor pipe idle,
+  // because the instruction queue behind the issuing thread is only an instruction or two deep.
+  static constexpr int ISSUERS = N_TILE >= 128 ? 2 : 1;
   static constexpr bool TOK_ON_M = N_TILE == 128 && GEMM == 1;   // (GEMM2 measured slower un-swapped: its row stores scatter)
   static constexpr int A_BYTES = 128 * 128;
   static constexpr int B_BYTES = N_TILE * 128;
@@ -215,8 +220,8 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
       }
     }
     __syncwarp();   // block-wide barriers below need whole warps
-  } else if (warp == 1) {
-    // ------------------------------------------------------------------ UMMA issuer
+  } else if (warp == 1 || (C::ISSUERS == 2 && warp == 2)) {
+    // ------------------------------------------------------------------ UMMA issuer(s)
     // One thread; its loop is the critical path of the large-tile regimes (every instruction is
     // dependent-issue latency), so ring positions are kept incrementally and the descriptors are
     // formed with one add from constants.
@@ -232,6 +237,11 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
       for (int i = blockIdx.x; ok && i < items; i += gridDim.x) {
         const Item w = decode_item<GEMM, N_TILE>(i, split, aux);
         for (int kb = w.kb0; kb < w.kb1; kb += C::KPS, ++nst) {        // items span whole stages
+          if (C::ISSUERS == 2 && (nst & 1) != warp - 1) {               // the other issuer's stage
+            if (++stage == C::STAGES) { stage = 0; ph ^= 1u; }
+            if (++buf == C::NBUF) { buf = 0; bph ^= 1u; }
+            continue;
+          }
           TRACE_STAGE(1, nst, 4, 0);
           if (!mbar_wait(tempty_base + buf * 8, bph ^ 1u, abort_flag)) { ok = false; break; }
           TRACE_STAGE(1, nst, 4, 1);
