@@ -73,7 +73,7 @@ struct Cfg {
   // with one thread the waits and loop overhead between two stages (~500 cycles) leave the tensor pipe idle,
   // because the instruction queue behind the issuing thread is only an instruction or two deep.
   static constexpr int ISSUERS = N_TILE >= 128 ? 2 : 1;
-  static constexpr bool TOK_ON_M = N_TILE == 128 && GEMM == 1;   // (GEMM2 measured slower un-swapped: its row stores scatter)
+  static constexpr bool TOK_ON_M = N_TILE == 128 && GEMM == 1;   // (GEMM2 measures the same either way)
   static constexpr int A_BYTES = 128 * 128;
   static constexpr int B_BYTES = N_TILE * 128;
   static constexpr int KB_BYTES = A_BYTES + NTERMS * B_BYTES;           // operands of one K-block
@@ -430,10 +430,9 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
       if (etid == 0 && nitem < 16) TRACE(3, 34 + 4 * nitem);
       if constexpr (C::TOK_ON_M) {
         if (q * 32 + lane < w.valid) {      // one token row, 64 consecutive outputs
-          float4* out = reinterpret_cast<float4*>(a.out + (static_cast<size_t>(w.s) * n_sel_pad + w.row0 + q * 32 + lane) * C::M_TOTAL +
-                                                  w.m * 128 + h * C::CPW);
+          float* out = a.out + (static_cast<size_t>(w.s) * n_sel_pad + w.row0 + q * 32 + lane) * C::M_TOTAL + w.m * 128 + h * C::CPW;
 #pragma unroll
-          for (int j = 0; j < C::CPW / 4; ++j) out[j] = make_float4(acc[4 * j], acc[4 * j + 1], acc[4 * j + 2], acc[4 * j + 3]);
+          for (int j = 0; j < C::CPW / 8; ++j) st_global_v8(out + 8 * j, acc + 8 * j);   // whole 32-byte sectors
         }
       } else {
         float* out = a.out + (static_cast<size_t>(w.s) * n_sel_pad + w.row0 + h * C::CPW) * C::M_TOTAL + w.m * 128 +
