@@ -194,8 +194,12 @@ int pick_n_tile(int T) {
   }();
   if (forced == 16 || forced == 32 || forced == 64 || forced == 128 || forced == 256) return forced;
   // 256-token tiles (GEMM1 only) exist for experiments (MOE_B200_NTILE=256); with eight promotion warps
-  // they are slower than 128-token tiles (the read-back of 256 TMEM columns per K-block dominates)
-  return T <= 16 ? 16 : T <= 32 ? 32 : T <= 64 ? 64 : 128;
+  // they are slower than 128-token tiles (the read-back of 256 TMEM columns per K-block dominates).
+  // The tile is chosen for the rows an expert typically gets (T / 32 with balanced routing), not for the worst
+  // case: an expert with more rows simply takes several tiles.  Measured on balanced batches: 32-token tiles
+  // win up to T = 256, 64-token tiles up to T = 1024, 128-token tiles beyond; 33..64 tokens keep 64-token
+  // tiles, which also serve small batches that pile onto a few experts.
+  return T <= 16 ? 16 : T <= 32 ? 32 : T <= 64 ? 64 : T <= 256 ? 32 : T <= 1024 ? 64 : 128;
 }
 
 // Decode path selection (MOE_B200_FUSED_DECODE): 1 = one launch (default), 0 = the general multi-kernel path.
