@@ -72,7 +72,7 @@ struct Cfg {
   // touch that stage's shared memory and TMEM columns and each thread commits its own, so stages are independent;
   // with one thread the waits and loop overhead between two stages (~500 cycles) leave the tensor pipe idle,
   // because the instruction queue behind the issuing thread is only an instruction or two deep.
-  static constexpr int ISSUERS = N_TILE >= 64 ? 2 : 1;
+  static constexpr int ISSUERS = N_TILE >= 32 ? 2 : 1;
   static constexpr bool TOK_ON_M = N_TILE == 128 && GEMM == 1;   // (GEMM2 measures the same either way)
   static constexpr int A_BYTES = 128 * 128;
   static constexpr int B_BYTES = N_TILE * 128;
