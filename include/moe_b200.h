@@ -113,6 +113,12 @@ int moe_ep_dispatch_push(const uint8_t* hidden_states, const float* hidden_state
                          const float* routing_logits, int T, const int64_t* rec_token, int n_records,
                          const moe_ep_segment* segments, int n_segments, void* stream);
 
+/* Last step of the expert-parallel layer: output[t] = bf16(sum, in ascending shard order and in fp32, of the
+ * bf16 rows back_rows[row_of[t][s]] for the shards s = 0..7 with row_of[t][s] >= 0).  The order and the
+ * arithmetic are those in which the layer reference sums the eight shard outputs
+ * (full-agent-pipeline/references/moe.py:196-200 per shard; the reference has no multi-rank code). */
+int moe_ep_sum_shards(const uint16_t* back_rows, const int32_t* row_of, int T, uint16_t* output, void* stream);
+
 /* Waits for `stream` and returns the error bits the kernels of the last call on
  * this workspace recorded (0 = none) in *status.  The reference checks no CUDA
  * return code at all (moe.cu:2729-2894); this is the replacement's error channel. */

@@ -50,6 +50,51 @@ __global__ void __launch_bounds__(128) ep_dispatch_push_kernel(const uint8_t* __
   }
 }
 
+// Final accumulation of the expert-parallel layer: out[t] = bf16(sum over shards s = 0..7, ascending, of
+// fp32(back[pos[t][s]])) for the shards the token selected (pos >= 0).  One block per token; replaces
+// eight index_add_ passes over fp32 copies of the returned rows.
+__global__ void __launch_bounds__(224) ep_sum_shards_kernel(const uint16_t* __restrict__ back,
+                                                            const int32_t* __restrict__ pos, int T,
+                                                            uint16_t* __restrict__ out) {
+  griddep_launch_dependents();
+  griddep_wait();
+  constexpr int kChunks = kH * 2 / 16;           // 896 x 16 B per row = 4 per thread
+  for (int t = blockIdx.x; t < T; t += gridDim.x) {
+    float acc[4][8];
+#pragma unroll
+    for (int c = 0; c < 4; ++c)
+#pragma unroll
+      for (int i = 0; i < 8; ++i) acc[c][i] = 0.0f;
+    for (int s = 0; s < 8; ++s) {
+      const int row = pos[t * 8 + s];
+      if (row < 0) continue;
+      const uint4* src = reinterpret_cast<const uint4*>(back + static_cast<size_t>(row) * kH);
+      uint4 v[4];
+#pragma unroll
+      for (int c = 0; c < 4; ++c) v[c] = src[threadIdx.x + c * 224];
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        const uint32_t w[4] = {v[c].x, v[c].y, v[c].z, v[c].w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          acc[c][2 * i] += __uint_as_float(w[i] << 16);
+          acc[c][2 * i + 1] += __uint_as_float(w[i] & 0xFFFF0000u);
+        }
+      }
+    }
+    uint4* dst = reinterpret_cast<uint4*>(out + static_cast<size_t>(t) * kH);
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+      uint32_t w[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+        asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(w[i]) : "f"(acc[c][2 * i + 1]), "f"(acc[c][2 * i]));
+      dst[threadIdx.x + c * 224] = make_uint4(w[0], w[1], w[2], w[3]);
+    }
+  }
+  static_assert(kChunks == 4 * 224, "row chunks per thread");
+}
+
 }  // namespace
 }  // namespace moe
 
@@ -73,5 +118,17 @@ extern "C" int moe_ep_dispatch_push(const uint8_t* hidden_states, const float* h
   int blocks = n_records < 8 * kNumSMs ? n_records : 8 * kNumSMs;
   cudaError_t e = launch_pdl(ep_dispatch_push_kernel, dim3(blocks), dim3(128), 0, static_cast<cudaStream_t>(stream_v),
                              hidden_states, hidden_states_scale, routing_logits, T, rec_token, n_records, tab);
+  return e == cudaSuccess ? MOE_B200_OK : MOE_B200_ECUDA;
+}
+
+extern "C" int moe_ep_sum_shards(const uint16_t* back_rows, const int32_t* row_of, int T, uint16_t* output,
+                                 void* stream_v) {
+  if (T < 0) return MOE_B200_EINVAL;
+  if (T == 0) return MOE_B200_OK;
+  if (!back_rows || !row_of || !output) return MOE_B200_EINVAL;
+  if ((reinterpret_cast<uintptr_t>(back_rows) | reinterpret_cast<uintptr_t>(output)) & 15u) return MOE_B200_EINVAL;
+  const int blocks = T < 16 * kNumSMs ? T : 16 * kNumSMs;
+  cudaError_t e = launch_pdl(ep_sum_shards_kernel, dim3(blocks), dim3(224), 0, static_cast<cudaStream_t>(stream_v),
+                             back_rows, row_of, T, output);
   return e == cudaSuccess ? MOE_B200_OK : MOE_B200_ECUDA;
 }

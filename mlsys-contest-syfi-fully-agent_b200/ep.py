@@ -91,6 +91,38 @@ def build_plan(topk_idx: torch.Tensor, world: int, rank: int, group=None) -> Dis
     return DispatchPlan(token_lists, send_counts, recv_counts, counts, send_order)
 
 
+def sum_shards(plan: DispatchPlan, back: torch.Tensor, T: int) -> torch.Tensor:
+    """Layer output of this rank's tokens from the returned rows (send order: shard-major, ascending token):
+    fp32 sum in ascending shard order, one bf16 rounding.  On a GPU this is one kernel
+    (``moe_ep_sum_shards``); CPU tensors (the gloo tests of the host logic) take the same sum with torch."""
+    dev = back.device
+    if dev.type == "cuda":
+        from . import loader
+        row_of = torch.full((T, N_SHARDS), -1, dtype=torch.int32, device=dev)
+        pos = 0
+        for s in range(N_SHARDS):
+            toks = plan.token_lists[s]
+            n = int(toks.numel())
+            if n:
+                row_of[toks, s] = torch.arange(pos, pos + n, dtype=torch.int32, device=dev)
+            pos += n
+        out = torch.empty((T, H), dtype=torch.bfloat16, device=dev)
+        back = back.contiguous()
+        with torch.cuda.device(dev):
+            loader.check(loader.lib.moe_ep_sum_shards(back.data_ptr(), row_of.data_ptr(), int(T), out.data_ptr(),
+                                                      torch.cuda.current_stream(dev).cuda_stream))
+        return out
+    acc = torch.zeros((T, H), dtype=torch.float32, device=dev)
+    pos = 0
+    for s in range(N_SHARDS):
+        toks = plan.token_lists[s]
+        n = int(toks.numel())
+        if n:
+            acc.index_add_(0, toks, back[pos:pos + n].to(torch.float32))
+        pos += n
+    return acc.to(torch.bfloat16)
+
+
 def _all_to_all(out: torch.Tensor, inp: torch.Tensor, out_splits, in_splits, world: int, group=None):
     if world == 1:
         out.copy_(inp)
@@ -222,15 +254,7 @@ class ExpertParallelMoE:
         # ---- combine: rows travel back along the same splits; ascending-shard fp32 accumulation
         back = torch.empty((n_send, H), dtype=torch.bfloat16, device=dev)
         _all_to_all(back, recv_out, plan.send_counts, plan.recv_counts, world, self.group)
-        acc = torch.zeros((T, H), dtype=torch.float32, device=dev)
-        pos = 0
-        for s in range(N_SHARDS):
-            toks = plan.token_lists[s]
-            n = int(toks.numel())
-            if n:
-                acc.index_add_(0, toks, back[pos:pos + n].to(torch.float32))
-            pos += n
-        return acc.to(torch.bfloat16)
+        return sum_shards(plan, back, T)
 
 
 def _forward_p2p(self, plan: DispatchPlan, routing_logits, routing_bias, hidden_states, hidden_states_scale,
@@ -301,15 +325,7 @@ def _forward_p2p(self, plan: DispatchPlan, routing_logits, routing_bias, hidden_
     px.barrier()                                            # every result row has landed at its source
 
     back = px.back_view(n_send)
-    acc = torch.zeros((T, H), dtype=torch.float32, device=dev)
-    pos = 0
-    for s in range(N_SHARDS):
-        toks = plan.token_lists[s]
-        n = int(toks.numel())
-        if n:
-            acc.index_add_(0, toks, back[pos:pos + n].to(torch.float32))
-        pos += n
-    return acc.to(torch.bfloat16)
+    return sum_shards(plan, back, T)
 
 
 ExpertParallelMoE._forward_p2p = _forward_p2p

@@ -31,6 +31,7 @@ EXPORTS = [
     "moe_fp8_block_scale_quantize_activations",
     "moe_fp8_block_scale_run_rows",
     "moe_ep_dispatch_push",
+    "moe_ep_sum_shards",
 ]
 STATIC_MAX_TOKENS = 4096
 STAGES = ("route_permute", "gather", "gemm1", "swiglu_split", "gemm2", "combine")
@@ -94,6 +95,8 @@ def _load() -> ctypes.CDLL:
     lib.moe_fp8_block_scale_run_rows.argtypes = run_args
     lib.moe_ep_dispatch_push.restype = i32
     lib.moe_ep_dispatch_push.argtypes = [vp, vp, vp, i32, vp, i32, ctypes.POINTER(EpSegment), i32, vp]
+    lib.moe_ep_sum_shards.restype = i32
+    lib.moe_ep_sum_shards.argtypes = [vp, vp, i32, vp, vp]
     lib.moe_fp8_block_scale_launch_count.restype = ctypes.c_longlong
     lib.moe_fp8_block_scale_launch_count.argtypes = []
     lib.moe_fp8_block_scale_set_profiling.restype = i32
