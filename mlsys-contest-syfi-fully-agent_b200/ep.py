@@ -405,6 +405,37 @@ def bench_main(args):
         results[tr] = dict(ms_step=float(ms) / args.steps, launches=loader.launch_count() - l0,
                            rows=float(n_rows), rows_max=float(rows_max), digest=gen.digest(out))
         del layer
+    # ---- the same layer call from host buffers: this rank's token tensors come from pinned host memory
+    # and its output rows go back to pinned host memory inside the timed region
+    layer = ExpertParallelMoE(weights, rank, world, transport=transports[0])
+    pin = lambda t: t.cpu().pin_memory()
+    h_in = [pin(logits), pin(bias), pin(hidden.view(torch.uint8)), pin(hscale)]
+    d_in = [torch.empty_like(logits), torch.empty_like(bias), torch.empty_like(hidden.view(torch.uint8)),
+            torch.empty_like(hscale)]
+    h_out = torch.empty((T, H), dtype=torch.bfloat16).pin_memory()
+
+    def step_host():
+        for d, h in zip(d_in, h_in):
+            d.copy_(h, non_blocking=True)
+        o = layer.forward(d_in[0], d_in[1], d_in[2].view(torch.float8_e4m3fn), d_in[3], rsf)
+        h_out.copy_(o, non_blocking=True)
+
+    for _ in range(3):
+        step_host()
+    sync()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        step_host()
+    e1.record()
+    sync()
+    ms_host = torch.tensor([e0.elapsed_time(e1)], device=dev)
+    if world > 1:
+        dist.all_reduce(ms_host, op=dist.ReduceOp.MAX)
+    ms_host = float(ms_host) / args.steps
+    h2d = sum(t.numel() * t.element_size() for t in h_in)
+    d2h = h_out.numel() * h_out.element_size()
+    del layer
     assert op.kernel_status(device=dev) == 0
     if len(results) == 2:
         assert results["p2p"]["digest"] == results["nccl"]["digest"], "transports disagree"
@@ -431,7 +462,10 @@ def bench_main(args):
                                 "tokens_per_s": T_total / (results["nccl"]["ms_step"] * 1e-3)}
                                if "nccl" in results and transports[0] != "nccl" else None),
             "fp8_tflops_per_gpu": total_rows and (T_total * 8 * 88080384 / world) / (ms_step * 1e-3) / 1e12,
-            "e2e": None, "roofline": None, "cpu_baseline": None,
+            "e2e": {"value": T_total / (ms_host * 1e-3), "unit": "tokens/s", "ms_per_step": ms_host,
+                    "h2d_bytes_per_step": h2d * world, "d2h_bytes_per_step": d2h * world,
+                    "note": "every rank copies its token tensors from pinned host memory and its output rows back"},
+            "roofline": None, "cpu_baseline": None,
         }))
     if world > 1:
         dist.destroy_process_group()
