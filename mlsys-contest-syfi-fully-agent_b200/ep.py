@@ -76,8 +76,12 @@ def build_plan(topk_idx: torch.Tensor, world: int, rank: int, group=None) -> Dis
     shard_of = (topk_idx.long() // E_LOCAL)                                   # [T, 8]
     hit = torch.zeros((topk_idx.shape[0], N_SHARDS), dtype=torch.bool, device=dev)
     hit.scatter_(1, shard_of, True)
-    token_lists = [torch.nonzero(hit[:, s], as_tuple=False).squeeze(1) for s in range(N_SHARDS)]
-    my_counts = torch.tensor([t.numel() for t in token_lists], dtype=torch.int64, device=dev)
+    # one nonzero over the transposed mask gives (shard, token) pairs shard-major with ascending tokens:
+    # a single host synchronisation instead of one per shard
+    pairs = torch.nonzero(hit.t().contiguous(), as_tuple=False)              # [n, 2]
+    my_counts = hit.sum(dim=0, dtype=torch.int64)
+    bounds = [0] + torch.cumsum(my_counts, 0).tolist()
+    token_lists = [pairs[bounds[s]:bounds[s + 1], 1] for s in range(N_SHARDS)]
     gathered = [torch.zeros_like(my_counts) for _ in range(world)]
     if world > 1:
         dist.all_gather(gathered, my_counts, group=group)
@@ -87,7 +91,7 @@ def build_plan(topk_idx: torch.Tensor, world: int, rank: int, group=None) -> Dis
     per = N_SHARDS // world
     send_counts = [int(counts[rank, d * per:(d + 1) * per].sum()) for d in range(world)]
     recv_counts = [int(counts[src, rank * per:(rank + 1) * per].sum()) for src in range(world)]
-    send_order = torch.cat(token_lists) if token_lists else torch.zeros(0, dtype=torch.int64, device=dev)
+    send_order = pairs[:, 1].contiguous()
     return DispatchPlan(token_lists, send_counts, recv_counts, counts, send_order)
 
 
