@@ -67,7 +67,7 @@ def first_seed_with_local_expert(T, skew, offset):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", required=True, help="checkout of the reference repository")
     ap.add_argument("--cases", default=",".join(CASES))
     args = ap.parse_args()
     ref = load_reference(args.reference)
