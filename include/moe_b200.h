@@ -3,9 +3,15 @@
  *
  * Plain pointers and sizes only; every pointer is a DEVICE pointer unless its
  * name says host.  All functions return 0 on success or a negative MOE_B200_E*
- * code.  The library keeps no state between calls except a per-process cache
- * of TMA descriptors and kernel attributes (mutex protected); all scratch
- * memory is the caller's `workspace`.
+ * code.  Scratch memory is the caller's `workspace`.  What the library keeps itself:
+ * a per-process cache of TMA descriptors and kernel attributes (mutex protected);
+ * one 256 KB pinned host block per calling thread of ..._run_host (allocated on its
+ * first small-batch call); and the fixed ~160 KB device array of
+ * ..._route_static (part of the library image on every GPU that loads it).
+ *
+ * Alignment (checked, MOE_B200_EINVAL otherwise): routing_logits, hidden_states,
+ * both weight tensors and output 16 bytes; workspace 1024 bytes; scales 4 bytes;
+ * routing_bias 2 bytes.
  */
 #ifndef MOE_B200_H_
 #define MOE_B200_H_
@@ -42,7 +48,13 @@ size_t moe_fp8_block_scale_workspace_bytes(int T);
  *   output                bf16 [T, 7168]        fully overwritten
  * Asynchronous on `stream` (a cudaStream_t); never synchronises with the host,
  * whatever T is (the reference blocks the host for T >= 512, moe.cu:2755-2759).
- * T == 0 returns at once, like the reference (moe.cu:2664). */
+ * T == 0 returns at once, like the reference (moe.cu:2664).
+ * T <= 16 runs as ONE persistent kernel of one CTA per SM whose phases meet at
+ * grid-wide barriers; it needs every SM of the device to itself.  A kernel of
+ * another stream (or process) that holds SMs for the whole call keeps some of its
+ * CTAs from starting: the barrier waits then run out after 0.4 s and the call
+ * ends with the error bits set (..._status returns MOE_B200_EKERNEL) -- no hang,
+ * but no result either.  Keep decode-sized calls alone on the device. */
 int moe_fp8_block_scale_run(const float* routing_logits, const uint16_t* routing_bias,
                             const uint8_t* hidden_states, const float* hidden_states_scale,
                             const uint8_t* gemm1_weights, const float* gemm1_weights_scale,

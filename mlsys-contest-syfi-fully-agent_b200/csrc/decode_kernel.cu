@@ -2,7 +2,7 @@
 // weighted combine in ONE persistent kernel, one CTA per SM.
 //
 // Replaces, for small batches, the whole launch sequence of the reference's run()
-// (moe/solution/cuda/moe.cu:2791-3090: route, histogram, scan, scatter, gather, two grouped GEMMs,
+// (moe/solution/cuda/moe.cu:2650-2896: route, histogram, scan, scatter, gather, two grouped GEMMs,
 // activation and combine kernels); arithmetic contract from full-agent-pipeline/references/moe.py:95-200.
 //
 // The operator is a stream of 44 MB of fp8 weights per active expert.  With a kernel per GEMM the
@@ -48,6 +48,7 @@ namespace moe {
 namespace {
 
 constexpr int kNT = kFusedMaxTokens;   // all tokens are one token tile
+constexpr int kL2PrefetchStages = 12;  // GEMM2 weight stages (32 KB each) a CTA asks into L2 behind its ring: <= 57 MB per GPU
 
 struct DC {
   static constexpr int KPS = kDecodeKps;                  // K-blocks per stage
@@ -380,11 +381,6 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_w1, const __grid_constant__
   __syncthreads();
   tc_fence_after_sync();
   const int tiles = fa->tiles;
-  // a tile has at most n / tiles-of-the-GEMM + 2 pieces; the SwiGLU phase sums up to 8 slabs, the combine 6
-  if (threadIdx.x == 0 && tiles > 0 &&
-      (static_cast<int>(gridDim.x) / (tiles * kMT1) + 2 > 8 || static_cast<int>(gridDim.x) / (tiles * kMT2) + 2 > 6)) {
-    atomicOr(&sched->status, kErrSchedOverflow);
-  }
   const int n_sel_pad = fa->n_sel_pad;
   const uint32_t tmem_base = aux->tmem_base;
   volatile int* abort_flag = &aux->abort;
@@ -432,6 +428,23 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_w1, const __grid_constant__
           if (ready ? ahead > 0 : (ahead == DC::STAGES || !whave)) {
             if (!ready) {
               DTRACE(1, 1);
+              // The ring is full of GEMM2 weights and HBM would now idle until the planes exist (two grid
+              // barriers and the SwiGLU phase away): ask for the weight boxes behind the ring into L2, so that
+              // after the barrier they arrive at L2 latency.  Bounded so that the slabs and planes stay in L2 too.
+              {
+                Part<2> ppart = wpart;
+                DItem pw = ww;
+                bool phave = whave;
+                int pkb = wkb;
+                for (int n = 0; phave && n < kL2PrefetchStages; ++n) {
+                  tma_prefetch_l2_3d(&tm_w2, 0, pw.e * kH + pw.m * 128, pkb);
+                  pkb += DC::KPS;
+                  if (pkb >= pw.kb1) {
+                    phave = ppart.next(aux, pw);
+                    pkb = pw.kb0;
+                  }
+                }
+              }
               if (!grid_barrier_wait(bar, a.g.call_tag, 2 * n_ctas)) { *abort_flag = 1; ok = false; break; }
               fence_proxy_async_global();   // the planes were written with ordinary stores by other SMs
               ready = true;
@@ -616,6 +629,9 @@ int decode_kernel_init() {
 
 int launch_decode(const CUtensorMap& tm_w1, const CUtensorMap& tm_x, const CUtensorMap& tm_w2, const CUtensorMap& tm_c,
                   const GemmArgs& g, const float* w2_scale, float* o, int ctas, cudaStream_t stream) {
+  // A weight-row tile is cut into at most ctas / (tiles of its GEMM) + 2 pieces, and there is at least one
+  // token tile; the SwiGLU phase sums up to 8 slabs (32 tiles per expert) and the combine up to 6 (56 tiles).
+  if (ctas < 1 || ctas / kMT1 + 2 > 8 || ctas / kMT2 + 2 > 6) return static_cast<int>(cudaErrorInvalidConfiguration);
   DecodeArgs a{g, w2_scale, o};
   return static_cast<int>(launch_pdl(decode_kernel, dim3(ctas), dim3(kGemmThreads), DC::SMEM_BYTES, stream, tm_w1, tm_x,
                                      tm_w2, tm_c, a));

@@ -116,6 +116,12 @@ struct CombineArgs {
   uint16_t* const* out_rows;    // optional: destination of every token's row (may be peer memory)
 };
 
+// Shared by every translation unit with an entry point: the calling thread's last cudaError_t (what
+// moe_fp8_block_scale_last_cuda_error returns) and the library's launch counter.
+void set_last_cuda_error(int cuda_error);
+void count_launches(int n);
+int route_permute_launches(int T);   // kernels launch_route_permute starts for T tokens
+
 void launch_route_permute(const RouteArgs& r, const PermuteArgs& p, cudaStream_t stream);
 void launch_route_only(const RouteArgs& r, cudaStream_t stream);
 void launch_gather_rows(const GatherArgs& a, int T, cudaStream_t stream);

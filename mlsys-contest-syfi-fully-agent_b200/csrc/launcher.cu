@@ -212,8 +212,15 @@ int fused_decode_mode() {
 }
 
 bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+bool aligned4(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 3u) == 0; }
+bool aligned2(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 1u) == 0; }
 
 }  // namespace
+
+void set_last_cuda_error(int cuda_error) { g_last_cuda_error = cuda_error; }
+void count_launches(int n) { g_launches += n; }
+int route_permute_launches(int T) { return T <= 32 ? 1 : T <= 1024 ? 2 : 3; }
+
 }  // namespace moe
 
 using namespace moe;
@@ -261,8 +268,10 @@ static int run_impl(const float* routing_logits, const uint16_t* routing_bias, c
   if (!routing_logits || !routing_bias || !hidden_states || !hidden_states_scale || !gemm1_weights ||
       !gemm1_weights_scale || !gemm2_weights || !gemm2_weights_scale || (!output && !output_rows) || !workspace)
     return MOE_B200_EINVAL;
-  if (!aligned16(hidden_states) || !aligned16(gemm1_weights) || !aligned16(gemm2_weights) || !aligned16(output) ||
-      (reinterpret_cast<uintptr_t>(workspace) & 1023u) != 0)
+  // vector loads and TMA: 16 bytes for the logits, the fp8 tensors and the output; natural alignment for the rest
+  if (!aligned16(routing_logits) || !aligned16(hidden_states) || !aligned16(gemm1_weights) || !aligned16(gemm2_weights) ||
+      !aligned16(output) || !aligned2(routing_bias) || !aligned4(hidden_states_scale) || !aligned4(gemm1_weights_scale) ||
+      !aligned4(gemm2_weights_scale) || (reinterpret_cast<uintptr_t>(workspace) & 1023u) != 0)
     return MOE_B200_EINVAL;
   if (workspace_bytes < moe_fp8_block_scale_workspace_bytes(T)) return MOE_B200_EWORKSPACE;
   DeviceState* dev = nullptr;
@@ -333,7 +342,7 @@ static int run_impl(const float* routing_logits, const uint16_t* routing_bias, c
   stage_mark(0, stream);
   launch_route_permute(ra, pa, stream);
   MOE_CUDA(cudaGetLastError());
-  g_launches += T <= 32 ? 1 : T <= 1024 ? 2 : 3;
+  g_launches += route_permute_launches(T);
   stage_mark(1, stream);
 
   GatherArgs ga{sched, perm_token, hidden_states, hidden_states_scale, T, a_packed, a_scale_rows};
@@ -423,16 +432,37 @@ extern "C" int moe_fp8_block_scale_run_host(const float* routing_logits_host, co
   const size_t Tz = static_cast<size_t>(T);
   const size_t in_bytes = st.out - st.logits;     // logits | bias | hidden | scales are contiguous in the staging area
   if (in_bytes <= kPackLimit) {
-    // Small batches: one copy instead of four.  The inputs are packed into a pinned block owned by
-    // this thread (allocated once) at the offsets of the device staging area.
-    static thread_local uint8_t* pinned = nullptr;
-    if (pinned == nullptr) MOE_CUDA(cudaHostAlloc(reinterpret_cast<void**>(&pinned), kPackLimit, cudaHostAllocDefault));
-    MOE_CUDA(cudaStreamSynchronize(stream));        // the previous call's copy may still read the block
+    // Small batches: one copy instead of four.  The inputs are packed into one of two pinned blocks owned by
+    // this thread (allocated once) at the offsets of the device staging area.  The blocks alternate and each
+    // has an event recorded behind the copy that read it, so a call only ever waits for the copy of the call
+    // before the previous one, not for the stream.
+    struct PinnedPair {
+      uint8_t* block[2] = {nullptr, nullptr};
+      cudaEvent_t copied[2] = {nullptr, nullptr};
+      int next = 0;
+    };
+    static thread_local PinnedPair pairs[16];      // events belong to a device: one pair per device
+    int cur = 0;
+    MOE_CUDA(cudaGetDevice(&cur));
+    if (cur < 0 || cur >= 16) return MOE_B200_EINVAL;
+    PinnedPair& pp = pairs[cur];
+    if (pp.block[0] == nullptr) {
+      for (int b = 0; b < 2; ++b) {
+        MOE_CUDA(cudaHostAlloc(reinterpret_cast<void**>(&pp.block[b]), kPackLimit, cudaHostAllocDefault));
+        MOE_CUDA(cudaEventCreateWithFlags(&pp.copied[b], cudaEventDisableTiming));
+        MOE_CUDA(cudaEventRecord(pp.copied[b], stream));
+      }
+    }
+    const int b = pp.next;
+    pp.next ^= 1;
+    MOE_CUDA(cudaEventSynchronize(pp.copied[b]));
+    uint8_t* pinned = pp.block[b];
     std::memcpy(pinned, routing_logits_host, Tz * kEGlobal * 4);
     std::memcpy(pinned + (st.bias - st.logits), routing_bias_host, kEGlobal * 2);
     std::memcpy(pinned + (st.hidden - st.logits), hidden_states_host, Tz * kH);
     std::memcpy(pinned + (st.hscale - st.logits), hidden_states_scale_host, Tz * kKB1 * 4);
     MOE_CUDA(cudaMemcpyAsync(ws + st.logits, pinned, in_bytes, cudaMemcpyHostToDevice, stream));
+    MOE_CUDA(cudaEventRecord(pp.copied[b], stream));
   } else {
     MOE_CUDA(cudaMemcpyAsync(d_logits, routing_logits_host, Tz * kEGlobal * 4, cudaMemcpyHostToDevice, stream));
     MOE_CUDA(cudaMemcpyAsync(d_bias, routing_bias_host, kEGlobal * 2, cudaMemcpyHostToDevice, stream));

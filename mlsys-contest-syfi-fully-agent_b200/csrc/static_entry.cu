@@ -74,8 +74,12 @@ extern "C" int moe_fp8_block_scale_route_static(const float* routing_logits, con
   if (T == 0) return MOE_B200_OK;
   if (!routing_logits || !routing_bias || !topk_idx || !topk_w || !expert_offsets || !perm_token || !perm_weight)
     return MOE_B200_EINVAL;
+  if ((reinterpret_cast<uintptr_t>(routing_logits) & 15u) != 0) return MOE_B200_EINVAL;
   unsigned char* scratch = nullptr;
-  if (scratch_address(&scratch) != 0) return MOE_B200_ECUDA;
+  if (const int e = scratch_address(&scratch)) {
+    set_last_cuda_error(e);
+    return MOE_B200_ECUDA;
+  }
   cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
   MoeSched* sched = reinterpret_cast<MoeSched*>(scratch);
   uint32_t* local_mask = reinterpret_cast<uint32_t*>(scratch + kSchedBytes);
@@ -87,9 +91,14 @@ extern "C" int moe_fp8_block_scale_route_static(const float* routing_logits, con
   PermuteArgs pa{T, local_expert_offset, 128, 128, kNumSMs, 1, 1, rows_cap, rows_cap > kMinSlabRows ? rows_cap : kMinSlabRows,
                  local_mask, topk_idx, topk_w, sched, perm_token, perm_weight, tok_rows, chunk_base};
   launch_route_permute(ra, pa, stream);
-  if (cudaGetLastError() != cudaSuccess) return MOE_B200_ECUDA;
-  if (cudaMemcpyAsync(expert_offsets, sched->offs, (kELocal + 1) * sizeof(int), cudaMemcpyDeviceToDevice, stream) !=
-      cudaSuccess)
+  cudaError_t e = cudaGetLastError();
+  if (e == cudaSuccess) {
+    count_launches(route_permute_launches(T));
+    e = cudaMemcpyAsync(expert_offsets, sched->offs, (kELocal + 1) * sizeof(int), cudaMemcpyDeviceToDevice, stream);
+  }
+  if (e != cudaSuccess) {
+    set_last_cuda_error(static_cast<int>(e));
     return MOE_B200_ECUDA;
+  }
   return MOE_B200_OK;
 }

@@ -28,8 +28,10 @@ dispatch is ONE kernel that gathers, packs and stores each record straight into 
 receive area (``moe_ep_dispatch_push``), and the combine happens inside the shard operator's
 last kernel, which writes every result row directly into the source rank's receive area
 (``moe_fp8_block_scale_run_rows`` with peer destinations).  Between the phases the ranks meet
-at the symmetric-memory barrier.  Plain peer stores only: no multicast, no TMA on peer memory,
-and no kernel ever waits on a peer.
+at the symmetric-memory barrier (torch's barrier kernel, which waits for its peers' signals; every
+rank reaches it, see ``_forward_p2p``).  The operator's own kernels use plain peer stores only: no
+multicast (torch is told not to bind the buffer to a multicast object either), no TMA on peer
+memory, and none of them waits on a peer.
 
 ``local_op`` and ``route_fn`` are injectable so that the host-side logic can be
 tested with gloo on CPU ranks; the defaults are the CUDA operator and fail loudly
@@ -37,6 +39,7 @@ without the compiled library.
 """
 from __future__ import annotations
 
+import os
 from dataclasses import dataclass
 from typing import Callable, List, Optional, Sequence
 
@@ -68,31 +71,35 @@ class DispatchPlan:
     recv_counts: List[int]                 # rows received from each rank
     counts: torch.Tensor                   # [world, 8] host int64: counts[src, shard]
     send_order: torch.Tensor               # local token index of every sent row, in send-buffer order
+    send_shard: torch.Tensor               # shard of every sent row (same order)
+    tokens_per_rank: List[int]             # T_local of every rank (same table on every rank)
 
 
 def build_plan(topk_idx: torch.Tensor, world: int, rank: int, group=None) -> DispatchPlan:
-    """``topk_idx`` [T_local, 8] global expert ids of this rank's tokens."""
+    """``topk_idx`` [T_local, 8] global expert ids of this rank's tokens.  One host synchronisation:
+    the gathered [world, 9] table of per-shard counts and token counts."""
     dev = topk_idx.device
+    T = topk_idx.shape[0]
     shard_of = (topk_idx.long() // E_LOCAL)                                   # [T, 8]
-    hit = torch.zeros((topk_idx.shape[0], N_SHARDS), dtype=torch.bool, device=dev)
+    hit = torch.zeros((T, N_SHARDS), dtype=torch.bool, device=dev)
     hit.scatter_(1, shard_of, True)
-    # one nonzero over the transposed mask gives (shard, token) pairs shard-major with ascending tokens:
-    # a single host synchronisation instead of one per shard
+    # nonzero over the transposed mask gives (shard, token) pairs shard-major with ascending tokens
     pairs = torch.nonzero(hit.t().contiguous(), as_tuple=False)              # [n, 2]
-    my_counts = hit.sum(dim=0, dtype=torch.int64)
-    bounds = [0] + torch.cumsum(my_counts, 0).tolist()
-    token_lists = [pairs[bounds[s]:bounds[s + 1], 1] for s in range(N_SHARDS)]
-    gathered = [torch.zeros_like(my_counts) for _ in range(world)]
+    mine = torch.cat([hit.sum(dim=0, dtype=torch.int64), torch.tensor([T], dtype=torch.int64, device=dev)])
+    gathered = [torch.zeros_like(mine) for _ in range(world)]
     if world > 1:
-        dist.all_gather(gathered, my_counts, group=group)
+        dist.all_gather(gathered, mine, group=group)
     else:
-        gathered = [my_counts]
-    counts = torch.stack(gathered).cpu()                                      # [world, 8]
+        gathered = [mine]
+    table = torch.stack(gathered).cpu()                                       # [world, 9]
+    counts = table[:, :N_SHARDS].contiguous()
+    bounds = [0] + torch.cumsum(counts[rank], 0).tolist()
+    token_lists = [pairs[bounds[s]:bounds[s + 1], 1] for s in range(N_SHARDS)]
     per = N_SHARDS // world
     send_counts = [int(counts[rank, d * per:(d + 1) * per].sum()) for d in range(world)]
     recv_counts = [int(counts[src, rank * per:(rank + 1) * per].sum()) for src in range(world)]
-    send_order = pairs[:, 1].contiguous()
-    return DispatchPlan(token_lists, send_counts, recv_counts, counts, send_order)
+    return DispatchPlan(token_lists, send_counts, recv_counts, counts, pairs[:, 1].contiguous(),
+                        pairs[:, 0].contiguous(), [int(x) for x in table[:, N_SHARDS]])
 
 
 def sum_shards(plan: DispatchPlan, back: torch.Tensor, T: int) -> torch.Tensor:
@@ -103,13 +110,9 @@ def sum_shards(plan: DispatchPlan, back: torch.Tensor, T: int) -> torch.Tensor:
     if dev.type == "cuda":
         from . import loader
         row_of = torch.full((T, N_SHARDS), -1, dtype=torch.int32, device=dev)
-        pos = 0
-        for s in range(N_SHARDS):
-            toks = plan.token_lists[s]
-            n = int(toks.numel())
-            if n:
-                row_of[toks, s] = torch.arange(pos, pos + n, dtype=torch.int32, device=dev)
-            pos += n
+        n = int(plan.send_order.numel())
+        if n:       # send order is shard-major: row i of `back` belongs to (send_order[i], send_shard[i])
+            row_of[plan.send_order, plan.send_shard] = torch.arange(n, dtype=torch.int32, device=dev)
         out = torch.empty((T, H), dtype=torch.bfloat16, device=dev)
         back = back.contiguous()
         with torch.cuda.device(dev):
@@ -151,6 +154,8 @@ class PeerExchange:
         total = self.off_back + al(max_send_rows * H * 2)
         self.max_recv_rows, self.max_send_rows, self.n_logits = max_recv_rows, max_send_rows, n_logits
         if world > 1:
+            # plain peer stores only: keep torch from binding the buffer to an NVLink multicast object
+            os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
             import torch.distributed._symmetric_memory as symm
             self.buf = symm.empty(total, dtype=torch.uint8, device=device)
             grp = group if group is not None else dist.group.WORLD
@@ -196,6 +201,7 @@ class ExpertParallelMoE:
             route_fn = route_fn or (lambda lg, b, rsf: op.route(lg, b, 0, rsf)[0])
         self.local_op, self.route_fn = local_op, route_fn
         self.last_plan: Optional[DispatchPlan] = None
+        self.last_shard_rows: List[int] = []       # records each owned shard processed in the last call
 
     def forward(self, routing_logits, routing_bias, hidden_states, hidden_states_scale,
                 routed_scaling_factor: float) -> torch.Tensor:
@@ -234,9 +240,11 @@ class ExpertParallelMoE:
             for j, s in enumerate(self.shards):
                 seg_start[(src, j)] = pos
                 pos += int(plan.counts[src, s])
+        self.last_shard_rows = []
         for j, s in enumerate(self.shards):
             segs = [(seg_start[(src, j)], int(plan.counts[src, s])) for src in range(world)]
             n_s = sum(n for _, n in segs)
+            self.last_shard_rows.append(n_s)
             if n_s == 0:
                 continue
             if per == 1:
@@ -272,16 +280,22 @@ def _forward_p2p(self, plan: DispatchPlan, routing_logits, routing_bias, hidden_
     dev = hidden_states.device
     n_logits = routing_logits.shape[1]
     per = N_SHARDS // world
-    if self._px is None:
-        # capacities for equal token counts per rank: every token of every rank may select each of my shards
-        self._px = PeerExchange(rank, world, self.group, dev, max(1, T * world * per), max(1, T * N_SHARDS), n_logits)
-    px = self._px
-    counts = plan.counts                                    # [world, 8] host
+    counts = plan.counts                                    # [world, 8] host, identical on every rank
     totals = counts.sum(dim=0)                              # records per shard over all sources
+    # Capacity of the symmetric areas.  Every rank evaluates the SAME condition from the shared table (largest
+    # receive and send count over all ranks), so either all ranks (re)allocate together -- the rendezvous is
+    # collective -- or none does: no rank can fail alone in front of a barrier its peers are already waiting in.
+    need_recv = max(int(totals[d * per:(d + 1) * per].sum()) for d in range(world))
+    need_send = max(int(counts[r].sum()) for r in range(world))
+    if self._px is None or need_recv > self._px.max_recv_rows or need_send > self._px.max_send_rows:
+        t_max = max(plan.tokens_per_rank)
+        cap_recv = max(1, need_recv, t_max * world * per if self._px is None else 2 * need_recv)
+        cap_send = max(1, need_send, t_max * N_SHARDS if self._px is None else 2 * need_send)
+        self._px = None                                     # release the old areas first
+        self._px = PeerExchange(rank, world, self.group, dev, cap_recv, cap_send, n_logits)
+    px = self._px
     n_send = int(counts[rank].sum())
     n_recv = int(sum(int(totals[s]) for s in self.shards))
-    if n_recv > px.max_recv_rows or n_send > px.max_send_rows:
-        raise RuntimeError("symmetric receive area too small for this batch")
 
     def recv_row_base(d: int, s: int, src: int) -> int:
         """First row, in rank d's receive area, of the records that `src` sends for shard s (shard-major)."""
@@ -306,25 +320,35 @@ def _forward_p2p(self, plan: DispatchPlan, routing_logits, routing_bias, hidden_
             loader.check(loader.lib.moe_ep_dispatch_push(
                 hidden_states.data_ptr(), hidden_states_scale.data_ptr(), routing_logits.data_ptr(), int(T),
                 plan.send_order.data_ptr(), n_send, segs, nseg, torch.cuda.current_stream(dev).cuda_stream))
+    # Destination of every result row, for all of this rank's shards at once (receive-area order: shard-major,
+    # then source rank): the position of the row's record in the source rank's send order.  A handful of
+    # device operations on one small host table instead of a Python loop per (source, shard).
+    ptr_table = None
+    if n_recv:
+        seg_base, seg_cnt = [], []
+        for s in self.shards:
+            for src in range(world):
+                seg_base.append(px.ptrs[src] + px.off_back + int(counts[src, :s].sum()) * H * 2)
+                seg_cnt.append(int(counts[src, s]))
+        host = torch.tensor([seg_base, seg_cnt], dtype=torch.int64).pin_memory()
+        seg = host.to(dev, non_blocking=True)
+        seg_id = torch.repeat_interleave(torch.arange(seg.shape[1], device=dev), seg[1], output_size=n_recv)
+        start = torch.cumsum(seg[1], 0) - seg[1]
+        ptr_table = seg[0][seg_id] + (torch.arange(n_recv, device=dev) - start[seg_id]) * (H * 2)
     px.barrier()                                            # every record has landed
 
     recv_h, recv_s, recv_l = px.recv_views(n_recv)
     row0 = 0
+    self.last_shard_rows = []
     for j, s in enumerate(self.shards):
         n_s = int(totals[s])
+        self.last_shard_rows.append(n_s)
         if n_s:
             rows = slice(row0, row0 + n_s)
-            # destination of every result row: the position of its record in the source rank's send order
-            ptrs = []
-            for src in range(world):
-                n = int(counts[src, s])
-                if n:
-                    base = px.ptrs[src] + px.off_back + int(counts[src, :s].sum()) * H * 2
-                    ptrs.append(base + torch.arange(n, device=dev, dtype=torch.int64) * (H * 2))
             w = self.shard_weights[j]
             op.run_rows(recv_l[rows], routing_bias, recv_h[rows].view(torch.float8_e4m3fn),
                         recv_s[rows].t().contiguous(), w.gemm1_weights, w.gemm1_weights_scale, w.gemm2_weights,
-                        w.gemm2_weights_scale, E_LOCAL * s, routed_scaling_factor, torch.cat(ptrs))
+                        w.gemm2_weights_scale, E_LOCAL * s, routed_scaling_factor, ptr_table[rows])
         row0 += n_s
     px.barrier()                                            # every result row has landed at its source
 
@@ -343,133 +367,3 @@ def layer_reference(shard_run: Callable[[int], torch.Tensor]) -> torch.Tensor:
         o = shard_run(s).to(torch.float32)
         acc = o if acc is None else acc + o
     return acc.to(torch.bfloat16)
-
-
-# ---------------------------------------------------------------------------------------------
-# bench.py --gpus N (N > 1), one rank per GPU under torchrun
-# ---------------------------------------------------------------------------------------------
-def bench_main(args):
-    import json
-    import os
-
-    from . import gen, loader, op
-
-    rank = int(os.environ.get("RANK", "0"))
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
-    dev = torch.device("cuda", local_rank)
-    torch.cuda.set_device(dev)
-    if world > 1 and not dist.is_initialized():
-        dist.init_process_group("nccl", device_id=dev)
-    T_total = 16384
-    T = T_total // world
-    rsf = gen.ROUTED_SCALING_FACTOR
-    shards = shards_of_rank(rank, world)
-    weights = [gen.make_shard_weights(1000 + s, dev) for s in shards]
-    tok_all = gen.make_tokens(T_total, 0, dev)
-    sl = slice(rank * T, (rank + 1) * T)
-    logits = tok_all.routing_logits[sl].contiguous()
-    hidden = tok_all.hidden_states[sl].contiguous()
-    hscale = tok_all.hidden_states_scale[:, sl].contiguous()
-    bias = tok_all.routing_bias
-    del tok_all
-    transports = [os.environ.get("MOE_B200_EP_TRANSPORT", "p2p")]
-    if transports[0] == "p2p":
-        transports.append("nccl")          # also timed, reported beside the headline
-
-    def sync():
-        if world > 1:
-            dist.barrier()
-        torch.cuda.synchronize()
-
-    results = {}
-    for tr in transports:
-        layer = ExpertParallelMoE(weights, rank, world, transport=tr)
-
-        def step():
-            return layer.forward(logits, bias, hidden, hscale, rsf)
-
-        for _ in range(max(args.warmup, 3)):
-            step()
-        sync()
-        l0 = loader.launch_count()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
-        for _ in range(args.steps):
-            out = step()
-        e1.record()
-        sync()
-        ms = torch.tensor([e0.elapsed_time(e1)], device=dev)
-        n_rows = torch.tensor([float(sum(layer.last_plan.recv_counts))], device=dev)
-        rows_max = n_rows.clone()
-        if world > 1:
-            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
-            dist.all_reduce(rows_max, op=dist.ReduceOp.MAX)
-            dist.all_reduce(n_rows, op=dist.ReduceOp.SUM)
-        results[tr] = dict(ms_step=float(ms) / args.steps, launches=loader.launch_count() - l0,
-                           rows=float(n_rows), rows_max=float(rows_max), digest=gen.digest(out))
-        del layer
-    # ---- the same layer call from host buffers: this rank's token tensors come from pinned host memory
-    # and its output rows go back to pinned host memory inside the timed region
-    layer = ExpertParallelMoE(weights, rank, world, transport=transports[0])
-    pin = lambda t: t.cpu().pin_memory()
-    h_in = [pin(logits), pin(bias), pin(hidden.view(torch.uint8)), pin(hscale)]
-    d_in = [torch.empty_like(logits), torch.empty_like(bias), torch.empty_like(hidden.view(torch.uint8)),
-            torch.empty_like(hscale)]
-    h_out = torch.empty((T, H), dtype=torch.bfloat16).pin_memory()
-
-    def step_host():
-        for d, h in zip(d_in, h_in):
-            d.copy_(h, non_blocking=True)
-        o = layer.forward(d_in[0], d_in[1], d_in[2].view(torch.float8_e4m3fn), d_in[3], rsf)
-        h_out.copy_(o, non_blocking=True)
-
-    for _ in range(3):
-        step_host()
-    sync()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for _ in range(args.steps):
-        step_host()
-    e1.record()
-    sync()
-    ms_host = torch.tensor([e0.elapsed_time(e1)], device=dev)
-    if world > 1:
-        dist.all_reduce(ms_host, op=dist.ReduceOp.MAX)
-    ms_host = float(ms_host) / args.steps
-    h2d = sum(t.numel() * t.element_size() for t in h_in)
-    d2h = h_out.numel() * h_out.element_size()
-    del layer
-    assert op.kernel_status(device=dev) == 0
-    if len(results) == 2:
-        assert results["p2p"]["digest"] == results["nccl"]["digest"], "transports disagree"
-    if rank == 0:
-        head = results[transports[0]]
-        ms_step, total_rows, rows_max = head["ms_step"], head["rows"], head["rows_max"]
-        print(json.dumps({
-            "metric": "moe_tokens_per_second", "value": T_total / (ms_step * 1e-3), "unit": "tokens/s",
-            "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_step,
-            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "fp8_e4m3",
-            "data": "synthetic",
-            "config": {"workload": "ep_layer_t16384", "T": T_total, "tokens_per_rank": T, "experts": 256,
-                       "shards_per_rank": len(shards), "token_seed": 0, "weight_seeds": "1000 + shard",
-                       "transport": transports[0],
-                       "dispatch": "one push kernel into the owner's symmetric receive area over NVLink "
-                                   "(fp8 row + scales + logits per (token, shard))" if transports[0] == "p2p"
-                                   else "NCCL all_to_all_single",
-                       "combine": "written by the shard operator's last kernel into the source rank's receive area "
-                                  "(bf16 row per (token, shard))" if transports[0] == "p2p" else "NCCL all_to_all_single",
-                       "l2": "per-rank weights (>= 1.4 GB) exceed L2", "records_total": total_rows,
-                       "load_balance_bound": total_rows / world / rows_max},
-            "gpu_launches": int(head["launches"]),
-            "nccl_transport": ({"ms_per_step": results["nccl"]["ms_step"],
-                                "tokens_per_s": T_total / (results["nccl"]["ms_step"] * 1e-3)}
-                               if "nccl" in results and transports[0] != "nccl" else None),
-            "fp8_tflops_per_gpu": total_rows and (T_total * 8 * 88080384 / world) / (ms_step * 1e-3) / 1e12,
-            "e2e": {"value": T_total / (ms_host * 1e-3), "unit": "tokens/s", "ms_per_step": ms_host,
-                    "h2d_bytes_per_step": h2d * world, "d2h_bytes_per_step": d2h * world,
-                    "note": "every rank copies its token tensors from pinned host memory and its output rows back"},
-            "roofline": None, "cpu_baseline": None,
-        }))
-    if world > 1:
-        dist.destroy_process_group()

@@ -62,9 +62,20 @@ def _check(cond: bool, msg: str):
         raise ValueError(msg)
 
 
+_validated = {}     # signature of the last argument set that passed _validate, per entry point
+
+
 def _validate(routing_logits, routing_bias, hidden_states, hidden_states_scale, gemm1_weights, gemm1_weights_scale,
               gemm2_weights, gemm2_weights_scale, output, device_inputs: bool):
     T = routing_logits.shape[0]
+    # A serving loop calls with the same buffers again and again: an argument set whose addresses, dtypes and
+    # shapes equal the last validated one is not inspected a second time (the checks cost more host time
+    # than a decode step's launch).
+    args = (routing_logits, routing_bias, hidden_states, hidden_states_scale, gemm1_weights, gemm1_weights_scale,
+            gemm2_weights, gemm2_weights_scale, output)
+    sig = tuple((t.data_ptr(), t.dtype, t.shape) for t in args)
+    if _validated.get(device_inputs) == sig:
+        return T
     _check(routing_logits.dtype == torch.float32 and tuple(routing_logits.shape) == (T, E_GLOBAL),
            "routing_logits must be float32 [T, 256]")
     _check(routing_bias.dtype == torch.bfloat16 and routing_bias.numel() == E_GLOBAL, "routing_bias must be bfloat16 [256]")
@@ -92,6 +103,7 @@ def _validate(routing_logits, routing_bias, hidden_states, hidden_states_scale, 
         _check(t.is_contiguous(), f"{name} must be contiguous")
         on_device = name.startswith("gemm") or device_inputs
         _check(t.is_cuda == on_device, f"{name} must live on the {'GPU' if on_device else 'host'}")
+    _validated[device_inputs] = sig
     return T
 
 
@@ -211,63 +223,13 @@ def kernel_status(workspace: Optional[Workspace] = None, device=None) -> int:
     return st.value
 
 
-def _sum_slabs(arr, offset, sched, gemm, pad, width):
-    """fp32 result [pad, width] of one GEMM from its split-K slabs.  General path: `split` equal slabs.
-    Decode path (split == 0): a weight-row tile has as many slabs as the balanced partition cut it into
-    pieces (csrc/decode_kernel.cu: stage_owner / tile_pieces), computed here from the tile index alone."""
-    split = sched.split1 if gemm == 1 else sched.split2
-    if split > 0:
-        s = arr(offset, split * pad * width * 4, torch.float32, (split, pad, width))
-        return s.sum(dim=0) if split > 1 else s[0]
-    n, mt = sched.ctas, width // 128
-    u = (56 if gemm == 1 else 16) // 2                 # pipeline stages per tile
-    G = sched.tiles_total * mt * u
-    owner = lambda g: ((g + 1) * n - 1) // G
-    pieces = lambda tau: owner(tau * u + u - 1) - owner(tau * u) + 1
-    counts, offs = list(sched.counts), list(sched.offs)
-    active = [e for e in range(32) if counts[e] > 0]
-    smax = max(pieces(t) for t in range(len(active) * mt))
-    s = arr(offset, smax * pad * width * 4, torch.float32, (smax, pad, width))
-    res = torch.zeros(pad, width, dtype=torch.float32, device=s.device)
-    for ordinal, e in enumerate(active):
-        rows = slice(offs[e], offs[e + 1])
-        for m in range(mt):
-            cols = slice(m * 128, (m + 1) * 128)
-            for k in range(pieces(ordinal * mt + m)):   # slab order, as the kernel sums
-                res[rows, cols] += s[k, rows, cols]
-    return res
-
-
-def intermediates(T: int, workspace: Optional[Workspace] = None, device=None) -> dict:
-    """Host copies of the selection / permutation / per-stage arrays the last
-    call with ``T`` tokens left in the workspace (for parity tests)."""
+def read_schedule(T: int, workspace: Optional[Workspace] = None, device=None) -> "loader.Sched":
+    """Waits for the device and returns a host copy of the schedule block the last call with ``T``
+    tokens left in the workspace: error bits, rows, active experts, tile widths and split-K factors
+    the device chose, per-expert counts and offsets (``include/moe_b200.h``: ``moe_b200_sched``)."""
     dev = torch.device(device if device is not None else "cuda")
     ws = workspace or _default_workspace(dev)
     torch.cuda.synchronize(ws.device)
     L = loader.layout(T)
-
-    def arr(off, nbytes, dtype, shape):
-        return ws.view(off, nbytes).view(dtype).reshape(shape)
-
-    sched_raw = ws.view(L.sched, ctypes.sizeof(loader.Sched)).cpu().numpy().tobytes()
-    sched = loader.Sched.from_buffer_copy(sched_raw)
-    n_sel, pad = sched.n_sel, sched.n_sel_pad
-    out = dict(
-        sched=sched, layout=L, n_sel=n_sel,
-        counts=torch.tensor(list(sched.counts)), offs=torch.tensor(list(sched.offs)),
-        topk_idx=arr(L.topk_idx, T * 8 * 4, torch.int32, (T, 8)).cpu(),
-        topk_w=arr(L.topk_w, T * 8 * 4, torch.float32, (T, 8)).cpu(),
-        local_mask=arr(L.local_mask, T * 4, torch.int32, (T,)).cpu(),
-        perm_token=arr(L.perm_token, n_sel * 4, torch.int32, (n_sel,)).cpu(),
-        perm_weight=arr(L.perm_weight, n_sel * 4, torch.float32, (n_sel,)).cpu(),
-        tok_rows=arr(L.tok_rows, T * 8 * 4, torch.int32, (T, 8)).cpu(),
-    )
-    if n_sel > 0:
-        out["g1"] = _sum_slabs(arr, L.g1, sched, 1, pad, 4096)[:n_sel].cpu()
-        out["o"] = _sum_slabs(arr, L.o, sched, 2, pad, H)[:n_sel].cpu()
-        cq = arr(L.cq, L.n_terms * L.rows_cap * I, torch.float8_e4m3fn, (L.n_terms, L.rows_cap, I))[:, :n_sel]
-        cs = arr(L.c_scale, L.rows_cap * 16 * 4, torch.float32, (L.rows_cap, 16))[:n_sel]
-        c = cq.to(torch.float32).sum(dim=0).view(n_sel, 16, 128) * cs.unsqueeze(2)
-        out["c"] = c.view(n_sel, I).cpu()
-        out["a_packed"] = arr(L.a_packed, n_sel * H, torch.uint8, (n_sel, H)).cpu()
-    return out
+    raw = ws.view(L.sched, ctypes.sizeof(loader.Sched)).cpu().numpy().tobytes()
+    return loader.Sched.from_buffer_copy(raw)

@@ -186,30 +186,64 @@ def selection_sets_equal(idx_a: torch.Tensor, idx_b: torch.Tensor) -> torch.Tens
 
 
 def bf16_steps(a_bf16: torch.Tensor, b_bf16: torch.Tensor) -> torch.Tensor:
-    """Number of representable bf16 values between corresponding elements (0 = equal, 1 = adjacent)."""
-    ai = a_bf16.cpu().contiguous().view(torch.int16).to(torch.int32)
-    bi = b_bf16.cpu().contiguous().view(torch.int16).to(torch.int32)
+    """Number of representable bf16 values between corresponding elements (0 = equal, 1 = adjacent).
+    Computed on the device of ``a_bf16``."""
+    dev = a_bf16.device
+    ai = a_bf16.contiguous().view(torch.int16).to(torch.int32)
+    bi = b_bf16.to(dev).contiguous().view(torch.int16).to(torch.int32)
     ao = torch.where(ai < 0, -(ai & 0x7FFF), ai)
     bo = torch.where(bi < 0, -(bi & 0x7FFF), bi)
     return (ao - bo).abs()
 
 
+HARNESS_RTOL = 1e-2     # the contest harness's own acceptance test: |a - b| <= atol + rtol |b|, reported as the
+HARNESS_ATOL = 1e-2     # ratio of matched elements (full-agent-pipeline/run_pipeline.py:298-305)
+
+
 def output_metrics(out_bf16: torch.Tensor, ref_bf16: torch.Tensor, ref_f32: Optional[torch.Tensor] = None) -> dict:
-    """max-abs error relative to the reference RMS, cosine, and a census of
-    elements that differ by exactly one bf16 step (a rounding flip of the
-    final cast) versus more."""
-    a = out_bf16.to(torch.float32).cpu().double()
-    b = ref_bf16.to(torch.float32).cpu().double()
-    rms = float(torch.sqrt((b * b).mean())) if b.numel() else 0.0
-    diff = (a - b).abs()
-    max_abs = float(diff.max()) if diff.numel() else 0.0
-    denom = float(a.norm() * b.norm())
-    cos = float((a * b).sum() / denom) if denom > 0 else 1.0
+    """max-abs error relative to the reference RMS, cosine, a census of elements that differ by
+    exactly one bf16 step (a rounding flip of the final cast) versus more, and the harness's
+    matched-element ratio at rtol = atol = 1e-2.  Arithmetic in float64 on the device of
+    ``out_bf16`` (large batches are compared on the GPU; the numbers do not depend on where)."""
+    dev = out_bf16.device
+    ref_bf16 = ref_bf16.to(dev)
+    n = int(out_bf16.numel())
+    if n == 0:
+        return dict(rms=0.0, max_abs=0.0, max_abs_over_rms=0.0, cosine=1.0, n=0, n_diff=0, n_one_step=0,
+                    n_multi_step=0, max_steps=0, match_ratio=1.0)
+    sq = dot = na = 0.0
+    max_abs = max_f32 = 0.0
+    matched = 0
+    rows = max(1, (1 << 24) // max(1, out_bf16.shape[-1]))          # chunks of ~16 M elements bound the fp64 scratch
+    a2, b2 = out_bf16.reshape(-1, out_bf16.shape[-1]), ref_bf16.reshape(-1, out_bf16.shape[-1])
+    r2 = None if ref_f32 is None else ref_f32.to(dev).reshape(-1, out_bf16.shape[-1])
+    for r0 in range(0, a2.shape[0], rows):
+        a = a2[r0:r0 + rows].to(torch.float64)
+        b = b2[r0:r0 + rows].to(torch.float64)
+        d = (a - b).abs()
+        sq += float((b * b).sum())
+        na += float((a * a).sum())
+        dot += float((a * b).sum())
+        max_abs = max(max_abs, float(d.max()))
+        matched += int((d <= HARNESS_ATOL + HARNESS_RTOL * b.abs()).sum())
+        if r2 is not None:
+            max_f32 = max(max_f32, float((a - r2[r0:r0 + rows].to(torch.float64)).abs().max()))
+    rms = (sq / n) ** 0.5
+    denom = (na ** 0.5) * (sq ** 0.5)
+    cos = dot / denom if denom > 0 else 1.0
     ulp = bf16_steps(out_bf16, ref_bf16)
     m = dict(rms=rms, max_abs=max_abs, max_abs_over_rms=(max_abs / rms if rms > 0 else 0.0), cosine=cos,
-             n=int(a.numel()), n_diff=int((ulp > 0).sum()), n_one_step=int((ulp == 1).sum()),
-             n_multi_step=int((ulp > 1).sum()), max_steps=int(ulp.max()) if ulp.numel() else 0)
+             n=n, n_diff=int((ulp > 0).sum()), n_one_step=int((ulp == 1).sum()),
+             n_multi_step=int((ulp > 1).sum()), max_steps=int(ulp.max()), match_ratio=matched / n)
     if ref_f32 is not None:
-        r = ref_f32.cpu().double()
-        m["max_abs_vs_f32_over_rms"] = float((a - r).abs().max()) / rms if rms > 0 else 0.0
+        m["max_abs_vs_f32_over_rms"] = max_f32 / rms if rms > 0 else 0.0
     return m
+
+
+PARITY_KEYS = ("max_abs_over_rms", "cosine", "n", "n_diff", "n_one_step", "n_multi_step", "match_ratio",
+               "max_abs_vs_f32_over_rms")
+
+
+def parity_report(m: dict) -> dict:
+    """The subset of ``output_metrics`` that the benchmark prints with every measured row."""
+    return {k: m[k] for k in PARITY_KEYS if k in m}

@@ -23,6 +23,7 @@ import pytest
 import torch
 
 import moe_oracle
+import ws_readers
 
 pytestmark = pytest.mark.gpu
 
@@ -58,30 +59,34 @@ def bf16_step(x: torch.Tensor) -> torch.Tensor:
 
 
 def assert_output_close(out_bf16, ref_bf16, ref_f32, rms=None):
-    out = out_bf16.float().cpu().double()
-    ref = ref_bf16.float().cpu().double()
-    r32 = ref_f32.cpu().double()
-    if rms is None:
-        rms = float(torch.sqrt((r32 * r32).mean()))
+    """The bars of the module docstring; arithmetic on the device of ``out_bf16`` in row chunks."""
+    dev = out_bf16.device
+    ref_bf16, ref_f32 = ref_bf16.to(dev), ref_f32.to(dev)
     m = moe_oracle.output_metrics(out_bf16, ref_bf16, ref_f32)
-    print("parity:", json.dumps({k: m[k] for k in ("max_abs_over_rms", "cosine", "n", "n_diff", "n_one_step")}))
+    if rms is None:
+        rms = float(torch.sqrt((ref_f32.double() ** 2).mean())) if ref_f32.numel() else 0.0
+    print("parity:", json.dumps(moe_oracle.parity_report(m)))
     assert m["cosine"] >= TOL_COSINE
     if rms == 0.0:
-        assert float(out.abs().max()) == 0.0
+        assert float(out_bf16.float().abs().max()) == 0.0
         return m
-    err = (out - ref).abs()
-    literal_bad = err > TOL_MAX_ABS_OVER_RMS * rms
-    one_step = moe_oracle.bf16_steps(out_bf16, ref_bf16) == 1
-    assert bool((~literal_bad | one_step).all()), \
-        f"{int((literal_bad & ~one_step).sum())} elements beyond 2e-2 x RMS that are not single rounding flips"
-    f32_err = (out - r32).abs()
-    bound = 0.5 * bf16_step(out) + TOL_F32_DOMAIN_OVER_RMS * rms
-    assert bool((f32_err <= bound).all()), f"fp32-domain error {float((f32_err - bound).max())} over the bound"
+    steps = moe_oracle.bf16_steps(out_bf16, ref_bf16)
+    rows = max(1, (1 << 23) // out_bf16.shape[-1])
+    for r0 in range(0, out_bf16.shape[0], rows):
+        out = out_bf16[r0:r0 + rows].double()
+        err = (out - ref_bf16[r0:r0 + rows].double()).abs()
+        literal_bad = err > TOL_MAX_ABS_OVER_RMS * rms
+        one_step = steps[r0:r0 + rows] == 1
+        assert bool((~literal_bad | one_step).all()), \
+            f"{int((literal_bad & ~one_step).sum())} elements beyond 2e-2 x RMS that are not single rounding flips"
+        f32_err = (out - ref_f32[r0:r0 + rows].double()).abs()
+        bound = 0.5 * bf16_step(out) + TOL_F32_DOMAIN_OVER_RMS * rms
+        assert bool((f32_err <= bound).all()), f"fp32-domain error {float((f32_err - bound).max())} over the bound"
     return m
 
 
 def assert_selection_and_permutation(pkg, T, ref_topk_sorted, ref_counts, ref_offsets, ref_perm_token, ref_perm_weight):
-    im = pkg.op.intermediates(T)
+    im = ws_readers.intermediates(pkg, T, stages=T <= 1024)
     got = torch.sort(im["topk_idx"].long(), dim=1).values
     assert torch.equal(got, torch.as_tensor(ref_topk_sorted).long()), "expert selection differs"
     assert torch.equal(im["counts"].long(), torch.as_tensor(ref_counts).long())
@@ -148,6 +153,44 @@ def test_against_oracle(pkg, dev, W, T, seed, skew, offset):
     assert float(out[no_local.to(dev)].float().abs().max() if bool(no_local.any()) else 0.0) == 0.0
 
 
+@pytest.mark.parametrize("T,seed,offset", [(8192, 21, 0), (16384, 0, 0)])
+def test_large_batch_against_gpu_oracle(pkg, dev, W, T, seed, offset):
+    """Shard calls of the size one rank of the expert-parallel layer sees (8-24 k rows): 128-token tiles,
+    the multi-CTA permutation fill.  The oracle runs on the GPU in fp32 (TF32 off): same definition,
+    cuBLAS fp32 summation order instead of the CPU's."""
+    tok = pkg.gen.make_tokens(T, seed, dev)
+    out = run_op(pkg, tok, W, offset)
+    ref = moe_oracle.run_full(tok.routing_logits, tok.routing_bias, tok.hidden_states, tok.hidden_states_scale,
+                              W.gemm1_weights, W.gemm1_weights_scale, W.gemm2_weights, W.gemm2_weights_scale,
+                              offset, RSF)
+    im = assert_selection_and_permutation(pkg, T, torch.sort(ref.topk_idx.cpu(), dim=1).values, ref.counts,
+                                          ref.offsets, ref.perm_token, ref.perm_weight.cpu())
+    assert im["n_sel"] == int(ref.counts.sum()) and im["n_sel"] > 4000
+    assert_output_close(out, ref.output, ref.output_f32)
+
+
+def test_definition_on_gpu_against_definition_on_cpu(pkg, dev):
+    """How far apart are two faithful fp32 evaluations of the definition?  The oracle on the GPU (cuBLAS fp32,
+    TF32 off) against the oracle on the CPU, T = 64, skewed routing (512 rows).  Neither is the CUDA path; the
+    printed numbers show what the literal max-abs bar means for ANY implementation that does not share the
+    reference's fp32 summation order, and are the yardstick for the flip census of the other tests."""
+    T = 64
+    tok = pkg.gen.make_tokens(T, 0, dev, True)
+    active = list(range(16))
+    Wg = pkg.gen.make_shard_weights(0, dev, experts=active)
+    g = moe_oracle.run_full(tok.routing_logits, tok.routing_bias, tok.hidden_states, tok.hidden_states_scale,
+                            Wg.gemm1_weights, Wg.gemm1_weights_scale, Wg.gemm2_weights, Wg.gemm2_weights_scale, 0, RSF)
+    assert sorted(int(e) for e in g.counts.nonzero().squeeze(1)) == active
+    cpu = lambda t: t.cpu()
+    c = moe_oracle.run(cpu(tok.routing_logits), cpu(tok.routing_bias), cpu(tok.hidden_states),
+                       cpu(tok.hidden_states_scale),
+                       lambda le: tuple(cpu(x[le]) for x in (Wg.gemm1_weights, Wg.gemm1_weights_scale,
+                                                              Wg.gemm2_weights, Wg.gemm2_weights_scale)), 0, RSF)
+    m = moe_oracle.output_metrics(g.output, c.output, c.output_f32)
+    print("oracle_gpu_vs_oracle_cpu:", json.dumps(moe_oracle.parity_report(m)))
+    assert m["cosine"] >= TOL_COSINE and m["n_multi_step"] == 0
+
+
 def test_empty_batch_is_a_noop(pkg, dev, W):
     tok = pkg.gen.make_tokens(0, 0, dev)
     out = pkg.op.run(tok.routing_logits, tok.routing_bias, tok.hidden_states, tok.hidden_states_scale,
@@ -211,7 +254,7 @@ def test_fp8_umma_accumulation_known_answer(pkg, dev, W):
     pkg.op.run(logits, bias, hs, hscale, W.gemm1_weights, W.gemm1_weights_scale, W.gemm2_weights,
                W.gemm2_weights_scale, 0, RSF)
     assert pkg.op.kernel_status() == 0
-    im = pkg.op.intermediates(T)
+    im = ws_readers.intermediates(pkg, T)
     assert int(im["counts"][3]) == T
     rows = slice(int(im["offs"][3]), int(im["offs"][4]))
     w = W.gemm1_weights[3].double().view(32, 128, 56, 128) * W.gemm1_weights_scale[3].double()[:, None, :, None]

@@ -11,6 +11,8 @@ The file name makes pytest collect it last."""
 import pytest
 import torch
 
+import ws_readers
+
 pytestmark = pytest.mark.gpu
 
 
@@ -40,7 +42,7 @@ def test_static_routing_matches_workspace_entry_point(pkg):
         pkg.op.run(tok.routing_logits, tok.routing_bias, tok.hidden_states, tok.hidden_states_scale,
                    W.gemm1_weights, W.gemm1_weights_scale, W.gemm2_weights, W.gemm2_weights_scale, off, rsf)
         assert pkg.op.kernel_status() == 0
-        im = pkg.op.intermediates(T)
+        im = ws_readers.intermediates(pkg, T, stages=False)
         n = im["n_sel"]
         assert torch.equal(idx, im["topk_idx"])
         assert torch.equal(w, im["topk_w"])
