@@ -260,12 +260,14 @@ def oracle_check(oracle, tok, W, out, T):
     return rep, ref
 
 
-def gemm_rooflines(sched, stage_us, P, name=None):
+def gemm_rooflines(sched, stage_us, P, large=False, fast_combine=False):
     """Roofline blocks of the two grouped GEMM launches of the general path from the stage events."""
-    g1 = roofline(f"grouped_gemm_kernel<1,{sched.n_tile}>", sched.n_active * W13_BYTES + sched.n_sel * ROW_BYTES,
-                  sched.n_sel * FLOPS1, stage_us["gemm1"], None, P)
-    g2 = roofline(f"grouped_gemm_kernel<2,{sched.n_tile2}>", sched.n_active * W2_BYTES, sched.n_sel * FLOPS2,
-                  stage_us["gemm2"], None, P)
+    k1 = "grouped_gemm_large_kernel<1> (GEMM1 + SwiGLU + e4m3 plane split)" if large else \
+        f"grouped_gemm_kernel<1,{sched.n_tile}>"
+    k2 = ("grouped_gemm_large_kernel<2,combine> (GEMM2 + routing weight + fp32 combine + bf16 cast)" if fast_combine
+          else "grouped_gemm_large_kernel<2>") if large else f"grouped_gemm_kernel<2,{sched.n_tile2}>"
+    g1 = roofline(k1, sched.n_active * W13_BYTES + sched.n_sel * ROW_BYTES, sched.n_sel * FLOPS1, stage_us["gemm1"], None, P)
+    g2 = roofline(k2, sched.n_active * W2_BYTES, sched.n_sel * FLOPS2, stage_us["gemm2"], None, P)
     return g1, g2
 
 
@@ -282,8 +284,18 @@ def profile_stages(loader, step, n):
     return {k: v / n * 1e3 for k, v in acc.items()}
 
 
-def measure_workload(pkg, oracle, W, name, steps, warmup, P, nprof=10):
-    """One single-GPU workload: tokens/s with resident inputs, per-stage times, roofline, parity."""
+def measure_workload(pkg, oracle, W, name, steps, warmup, P, nprof=10, options=0):
+    """One single-GPU workload: tokens/s with resident inputs, per-stage times, roofline, parity.
+    `options`: operator options (MOE_B200_OPT_*) in force for this measurement only."""
+    gen, op, loader = pkg.gen, pkg.op, pkg.loader
+    loader.set_options(options)
+    try:
+        return _measure_workload(pkg, oracle, W, name, steps, warmup, P, nprof, options)
+    finally:
+        loader.set_options(0)
+
+
+def _measure_workload(pkg, oracle, W, name, steps, warmup, P, nprof, options):
     gen, op, loader = pkg.gen, pkg.op, pkg.loader
     dev = W.gemm1_weights.device
     wl = WORKLOADS[name]
@@ -319,14 +331,17 @@ def measure_workload(pkg, oracle, W, name, steps, warmup, P, nprof=10):
                        us, NCU_TRAFFIC_BYTES.get(name), P)
         kernels = {}
     else:
-        g1, g2 = gemm_rooflines(sched, stage_us, P)
+        g1, g2 = gemm_rooflines(sched, stage_us, P, large=T > 1024 and not (options & loader.OPT_UNFUSED),
+                                fast_combine=bool(options & loader.OPT_FAST_COMBINE))
         dom = g1 if stage_us["gemm1"] >= stage_us["gemm2"] else g2
         dom["traffic"] = NCU_TRAFFIC_BYTES.get(name) if dom is g1 else None
         kernels = {"gemm1": g1, "gemm2": g2}
     step(0)       # leave `out` holding replica 0's result for the check
     torch.cuda.synchronize()
     parity, ref = oracle_check(oracle, tok, W, out, T)
-    row = {"workload": name, "T": T, "n_sel": sched.n_sel, "active_experts": sched.n_active, "replicas": R,
+    row = {"workload": name, "options": {"fast_combine": bool(options & loader.OPT_FAST_COMBINE),
+                                         "unfused": bool(options & loader.OPT_UNFUSED)},
+           "T": T, "n_sel": sched.n_sel, "active_experts": sched.n_active, "replicas": R,
            "us_per_step": us, "tokens_per_s": T / us * 1e6, "gpu_launches_per_step": launches // max(1, steps),
            "split_k": [sched.split1, sched.split2], "token_tile": [sched.n_tile, sched.n_tile2],
            "stage_us": stage_us, "roofline": dom, "whole_op": whole, "kernels": kernels, "parity": parity}
@@ -458,6 +473,10 @@ def bench_single(args):
                 r, c = measure_workload(pkg, oracle, W, n, 30, 5, P)
                 rows.append(r)
                 del c
+        # the large-batch path's two other modes on the prefill workload: combine fused into GEMM2's epilogue
+        # (not bit-reproducible), and the multi-kernel path without any epilogue fusion (A/B)
+        line["sweep_modes"] = [measure_workload(pkg, oracle, W, "prefill_t4096", 30, 5, P, options=o)[0]
+                               for o in (loader.OPT_FAST_COMBINE, loader.OPT_UNFUSED)]
         line["sweep"] = rows
         line["oracle_vs_oracle"] = oracle_vs_oracle(pkg, oracle, dev)
         del W, reps, ctx
@@ -692,7 +711,7 @@ def bench_ep(args):
         ms_step, total_rows, rows_max = head["ms_step"], head["rows"], head["rows_max"]
         stage_us = {k: v * 1e3 for k, v in stage_ms.items()}
         if shard_sched is not None:
-            g1, g2 = gemm_rooflines(shard_sched, stage_us, P)
+            g1, g2 = gemm_rooflines(shard_sched, stage_us, P, large=shard_rows > 1024)
             dom = g1 if stage_us["gemm1"] >= stage_us["gemm2"] else g2
             dom["scope"] = (f"one shard call on rank 0 (shard {shards[-1]}, {shard_rows} records, "
                             f"{shard_sched.n_sel} rows)")

@@ -10,8 +10,8 @@
  * ..._route_static (part of the library image on every GPU that loads it).
  *
  * Alignment (checked, MOE_B200_EINVAL otherwise): routing_logits, hidden_states,
- * both weight tensors and output 16 bytes; workspace 1024 bytes; scales 4 bytes;
- * routing_bias 2 bytes.
+ * both weight tensors, both weight-scale tensors and output 16 bytes; workspace
+ * 1024 bytes; hidden_states_scale 4 bytes; routing_bias 2 bytes.
  */
 #ifndef MOE_B200_H_
 #define MOE_B200_H_
@@ -158,6 +158,8 @@ typedef struct moe_b200_layout {
   uint64_t cq;           /* e4m3 [n_terms][rows_cap, 2048] SwiGLU planes     */
   uint64_t c_scale;      /* f32 [rows_cap, 16]                               */
   uint64_t o;            /* f32 [split2][n_sel_pad, 7168] GEMM2 slabs        */
+  uint64_t acc32;        /* f32 [T, 7168] output accumulator (fast combine)  */
+  uint64_t tile_cnt;     /* i32 [T, 56] arrivals per (token, column tile)    */
   uint64_t total;        /* == moe_fp8_block_scale_workspace_bytes(T)        */
 } moe_b200_layout;
 
@@ -172,6 +174,22 @@ typedef struct moe_b200_sched {
 } moe_b200_sched;
 
 int moe_fp8_block_scale_layout(int T, moe_b200_layout* out);
+
+/* Process-wide options of the operator (default 0).
+ *  MOE_B200_OPT_FAST_COMBINE  For calls with more than 1024 tokens the GEMM2 epilogue multiplies by the routing
+ *    weight and adds straight into an fp32 [T, 7168] accumulator (vector reductions) and the last contributor of
+ *    every (token, 128-column tile) casts it to bf16: the scheme of the reference's own GEMM2 epilogue
+ *    (moe/solution/cuda/moe.cu:2404-2430, 2473-2496).  Faster, same tolerance, but the fp32 summation order is no
+ *    longer fixed: two runs may differ in the last bf16 bit of a few elements.  Without it the combine is a
+ *    separate kernel that sums a token's experts in ascending order (bit-reproducible; the order of
+ *    full-agent-pipeline/references/moe.py:196-200).
+ *  MOE_B200_OPT_UNFUSED  Calls with more than 1024 tokens take the same multi-kernel path as smaller ones (GEMM1 ->
+ *    SwiGLU kernel -> GEMM2 -> combine kernel) instead of the large-batch kernels that fuse SwiGLU into GEMM1's
+ *    epilogue.  For A/B measurements and for tests that compare the two paths bit for bit. */
+#define MOE_B200_OPT_FAST_COMBINE 1u
+#define MOE_B200_OPT_UNFUSED 2u
+int moe_fp8_block_scale_set_options(unsigned int options);
+unsigned int moe_fp8_block_scale_get_options(void);
 
 /* Kernels launched by this library since it was loaded (all threads). */
 long long moe_fp8_block_scale_launch_count(void);

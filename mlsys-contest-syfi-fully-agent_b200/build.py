@@ -17,7 +17,7 @@ CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libmoe_b200.so")
 LIB_TVMFFI = os.path.join(HERE, "libmoe_b200_tvmffi.so")
 
-SOURCES = ["launcher.cu", "route_permute.cu", "grouped_gemm.cu", "decode_kernel.cu", "swiglu_combine.cu", "static_entry.cu", "quantize.cu", "ep_push.cu"]
+SOURCES = ["launcher.cu", "route_permute.cu", "grouped_gemm.cu", "grouped_gemm_large.cu", "decode_kernel.cu", "swiglu_combine.cu", "static_entry.cu", "quantize.cu", "ep_push.cu"]
 HEADERS = ["kernels.h", "moe_layout.h", "ptx.cuh", "route_device.cuh", "epilogue_device.cuh", "gemm_common.cuh", os.path.join("..", "..", "include", "moe_b200.h")]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-lineinfo", "-std=c++17",
               "-shared", "-Xcompiler", "-fPIC"]

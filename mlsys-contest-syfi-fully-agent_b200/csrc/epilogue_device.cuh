@@ -15,25 +15,47 @@ __device__ __forceinline__ float from_e4m3(uint8_t b) {
   return __half2float(__half(h));
 }
 
-// SwiGLU of 4 columns per lane of one (row, 128-column block), split of the result into kNTerms e4m3
-// planes with one power-of-two scale for the block.
-__device__ __forceinline__ void swiglu_finish_block(const float4 x1, const float4 x2, int row, int kb, int lane, uint8_t* cq,
-                                                    float* c_scale, int rows_cap) {
-  float c[4];
-  c[0] = __fmul_rn(x2.x / (1.0f + expf(-x2.x)), x1.x);
-  c[1] = __fmul_rn(x2.y / (1.0f + expf(-x2.y)), x1.y);
-  c[2] = __fmul_rn(x2.z / (1.0f + expf(-x2.z)), x1.z);
-  c[3] = __fmul_rn(x2.w / (1.0f + expf(-x2.w)), x1.w);
-  float amax = fmaxf(fmaxf(fabsf(c[0]), fabsf(c[1])), fmaxf(fabsf(c[2]), fabsf(c[3])));
-#pragma unroll
-  for (int d = 16; d > 0; d >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, d));
-  // power-of-two scale 2^e with amax / scale in (224, 448]: e = floor(log2(amax / 448)) + 1, clamped to
-  // [-100, 100]; read from the exponent field (a denormal quotient clamps to -100 either way)
+// One element of the SwiGLU output: C = silu(x2) * x1 with IEEE exp and division
+// (full-agent-pipeline/references/moe.py:187-193: the second half of GEMM1's result goes through silu).
+__device__ __forceinline__ float swiglu_value(float x1, float x2) {
+  return __fmul_rn(x2 / (1.0f + expf(-x2)), x1);
+}
+
+// Exponent e of the power-of-two plane scale 2^e of a 128-column block with |C| maximum `amax`:
+// amax / 2^e lies in (224, 448]: e = floor(log2(amax / 448)) + 1, clamped to [-100, 100]; read from the
+// exponent field (a denormal quotient clamps to -100 either way).  0 for an all-zero or non-finite block.
+__device__ __forceinline__ int plane_scale_exponent(float amax) {
   int e = 0;
   if (amax > 0.0f && amax < 3.0e38f) {
     e = static_cast<int>((__float_as_uint(amax * (1.0f / 448.0f)) >> 23) & 0xFFu) - 127 + 1;
     e = max(-100, min(100, e));
   }
+  return e;
+}
+
+// r (already divided by the plane scale) as kNTerms e4m3 terms: t_i = e4m3(residual after t_0 .. t_{i-1}).
+__device__ __forceinline__ void split_e4m3_terms(float r, uint8_t* t) {
+  if (!(fabsf(r) <= 448.0f)) r = r > 0.0f ? 448.0f : (r < 0.0f ? -448.0f : 0.0f);   // inf / nan guard
+#pragma unroll
+  for (int i = 0; i < kNTerms; ++i) {
+    t[i] = to_e4m3(r);
+    r -= from_e4m3(t[i]);
+  }
+}
+
+// SwiGLU of 4 columns per lane of one (row, 128-column block), split of the result into kNTerms e4m3
+// planes with one power-of-two scale for the block.
+__device__ __forceinline__ void swiglu_finish_block(const float4 x1, const float4 x2, int row, int kb, int lane, uint8_t* cq,
+                                                    float* c_scale, int rows_cap) {
+  float c[4];
+  c[0] = swiglu_value(x1.x, x2.x);
+  c[1] = swiglu_value(x1.y, x2.y);
+  c[2] = swiglu_value(x1.z, x2.z);
+  c[3] = swiglu_value(x1.w, x2.w);
+  float amax = fmaxf(fmaxf(fabsf(c[0]), fabsf(c[1])), fmaxf(fabsf(c[2]), fabsf(c[3])));
+#pragma unroll
+  for (int d = 16; d > 0; d >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, d));
+  const int e = plane_scale_exponent(amax);
   const float scale = __uint_as_float(static_cast<uint32_t>(e + 127) << 23);
   const float inv = __uint_as_float(static_cast<uint32_t>(127 - e) << 23);
   uint32_t packed[kNTerms];
@@ -41,14 +63,10 @@ __device__ __forceinline__ void swiglu_finish_block(const float4 x1, const float
   for (int t = 0; t < kNTerms; ++t) packed[t] = 0;
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
-    float r = c[i] * inv;
-    if (!(fabsf(r) <= 448.0f)) r = r > 0.0f ? 448.0f : (r < 0.0f ? -448.0f : 0.0f);   // inf / nan guard
+    uint8_t q[kNTerms];
+    split_e4m3_terms(c[i] * inv, q);
 #pragma unroll
-    for (int t = 0; t < kNTerms; ++t) {
-      const uint8_t q = to_e4m3(r);
-      r -= from_e4m3(q);
-      packed[t] |= static_cast<uint32_t>(q) << (8 * i);
-    }
+    for (int t = 0; t < kNTerms; ++t) packed[t] |= static_cast<uint32_t>(q[t]) << (8 * i);
   }
 #pragma unroll
   for (int t = 0; t < kNTerms; ++t)

@@ -112,6 +112,8 @@ __device__ __forceinline__ bool grid_barrier_wait(unsigned int* word2, unsigned 
 
 // K-blocks per pipeline stage of the decode kernel.
 constexpr int kDecodeKps = 2;
+// Up to this many tokens the decode kernel routes with one thread per expert (see decode_route_schedule).
+constexpr int kBlockRouteMaxTokens = 4;
 
 // CPW fp32 columns of this warp's 32 TMEM lanes -> registers.
 template <int CPW>
@@ -146,6 +148,86 @@ __device__ __forceinline__ void decode_route_schedule(const GemmArgs& a, uint8_t
   //     network), then five butterfly steps merge the lists: with the partner's list reversed, the element-wise
   //     maximum is the top 8 of both lists as a bitonic sequence, which a 3-stage merge network sorts.  After
   //     the last step every lane holds the selection in descending order.
+  if (a.T <= kBlockRouteMaxTokens) {
+    // A few tokens: thread = expert (warps 0..7, warp = routing group), one token after the other.  The sort
+    // networks below take ~2500 cycles whatever the batch; counting, for every kept expert, the kept experts
+    // that beat it takes a few hundred per token.  Same arithmetic and tie rules (route_block_kernel).
+    uint32_t* keys = reinterpret_cast<uint32_t*>(smem);             // the stage ring is still idle
+    float* gscore = reinterpret_cast<float*>(smem + 1024);
+    int* selidx = reinterpret_cast<int*>(smem + 1024 + 64);
+    float* sels = reinterpret_cast<float*>(smem + 1024 + 128);
+    if (warp < kNGroup) {
+      const int e = threadIdx.x;
+      float x[kBlockRouteMaxTokens];
+#pragma unroll
+      for (int t = 0; t < kBlockRouteMaxTokens; ++t)                 // all tokens' logits in flight
+        x[t] = t < a.T ? a.logits[static_cast<size_t>(t) * kEGlobal + e] : 0.0f;
+      const float bias_e = __uint_as_float(static_cast<uint32_t>(a.bias_bf16[e]) << 16);
+      if (threadIdx.x == 0) MOE_ROUTE_TRACE(0);
+#pragma unroll 1
+      for (int t = 0; t < a.T; ++t) {
+        float xt = x[0];
+#pragma unroll
+        for (int u = 1; u < kBlockRouteMaxTokens; ++u) xt = u == t ? x[u] : xt;
+        const float s_e = 1.0f / (1.0f + expf(-xt));
+        const uint32_t key_e = order_key(s_e + bias_e);
+        keys[e] = key_e;
+        const uint32_t k1 = __reduce_max_sync(0xFFFFFFFFu, key_e);
+        const int first = __ffs(__ballot_sync(0xFFFFFFFFu, key_e == k1)) - 1;
+        const uint32_t k2 = __reduce_max_sync(0xFFFFFFFFu, lane == first ? 0u : key_e);
+        const uint32_t u1 = (k1 & 0x80000000u) ? (k1 & 0x7FFFFFFFu) : ~k1;
+        const uint32_t u2 = (k2 & 0x80000000u) ? (k2 & 0x7FFFFFFFu) : ~k2;
+        if (lane == 0) gscore[warp] = __uint_as_float(u1) + __uint_as_float(u2);
+        named_bar_sync(1, kNGroup * 32);
+        uint32_t keep = 0;
+#pragma unroll
+        for (int g = 0; g < kNGroup; ++g) {
+          int rank = 0;
+#pragma unroll
+          for (int h = 0; h < kNGroup; ++h) rank += (gscore[h] > gscore[g]) || (gscore[h] == gscore[g] && h < g);
+          keep |= (rank < kTopKGroup ? 1u : 0u) << g;
+        }
+        if ((keep >> warp) & 1u) {
+          int rank = 0;
+          for (int g = 0; g < kNGroup; ++g) {
+            if (!((keep >> g) & 1u)) continue;
+            const uint4* kv = reinterpret_cast<const uint4*>(keys + g * 32);
+#pragma unroll
+            for (int c = 0; c < 8; ++c) {
+              const uint4 k = kv[c];
+              const int j = g * 32 + c * 4;
+              rank += (k.x > key_e) || (k.x == key_e && j + 0 < e);
+              rank += (k.y > key_e) || (k.y == key_e && j + 1 < e);
+              rank += (k.z > key_e) || (k.z == key_e && j + 2 < e);
+              rank += (k.w > key_e) || (k.w == key_e && j + 3 < e);
+            }
+          }
+          if (rank < kTopK) { selidx[rank] = e; sels[rank] = s_e; }
+        }
+        named_bar_sync(1, kNGroup * 32);
+        if (warp == 0) {
+          const float sv = lane < kTopK ? sels[lane] : 0.0f;
+          float sum = 0.0f;
+#pragma unroll
+          for (int k = 0; k < kTopK; ++k) sum += __shfl_sync(0xFFFFFFFFu, sv, k);   // selection order, like every other path
+          sum += 1e-20f;
+          uint32_t bit = 0;
+          if (lane < kTopK) {
+            const int idx = selidx[lane];
+            fa->tidx[t][lane] = idx;
+            fa->tw[t][lane] = (sv / sum) * a.routed_scaling_factor;
+            const int le = idx - a.local_expert_offset;
+            if (le >= 0 && le < kELocal) bit = 1u << le;
+          }
+          bit = __reduce_or_sync(0xFFFFFFFFu, bit);
+          if (lane == 0) fa->mask[t] = bit;
+        }
+        // the next token's keys / gscore are written before, selidx / sels after the next first barrier;
+        // warp 0 has read selidx / sels before it reaches that barrier
+      }
+    }
+    if (threadIdx.x == 0) MOE_ROUTE_TRACE(1);
+  } else {
   float* bias_s = fa->sval;
   for (int i = threadIdx.x; i < kEGlobal; i += kGemmThreads)
     bias_s[i] = __uint_as_float(static_cast<uint32_t>(a.bias_bf16[i]) << 16);
@@ -276,6 +358,7 @@ __device__ __forceinline__ void decode_route_schedule(const GemmArgs& a, uint8_t
     if (threadIdx.x == 0) MOE_ROUTE_CLK(12);
   }
   if (threadIdx.x == 0) MOE_ROUTE_TRACE(1);
+  }   // T > kBlockRouteMaxTokens
   fence_proxy_async_smem();   // the logits scratch is about to be overwritten by TMA (async proxy)
   __syncthreads();
   if (warp == 0) {                     // lane = local expert

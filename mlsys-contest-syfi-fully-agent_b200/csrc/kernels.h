@@ -62,6 +62,8 @@ struct PermuteArgs {
   float* perm_weight;           // [n_sel] combination weight of each row
   int* tok_rows;                // [T, 8] rows of a token in ascending local expert order
   int* chunk_base;              // [ceil(T / 32), 32] first row of every (32-token chunk, expert); large T only
+  int large;                    // 1: GEMM1 with the SwiGLU epilogue (no split-K, items are (token tile, 128-column block of C));
+                                // 2: also GEMM2 with the fused combine (no split-K either)
 };
 
 struct GatherArgs {
@@ -95,6 +97,9 @@ struct GemmArgs {
   uint8_t* cq; float* c_scale;  // SwiGLU planes and their scales
   uint16_t* out_bf16;           // final output
   uint16_t* const* out_rows;    // optional per-token destinations instead of out_bf16 (may be peer memory)
+  // ---- only read by the large-batch GEMM2 with the fused combine (grouped_gemm_large.cu)
+  float* acc32;                 // [T, 7168] fp32 accumulator of the output, zero before the launch
+  int* tile_cnt;                // [T, 56] contributions that have arrived per (token, 128-column tile), zero before
 };
 
 struct SwigluArgs {
@@ -125,7 +130,7 @@ int route_permute_launches(int T);   // kernels launch_route_permute starts for 
 void launch_route_permute(const RouteArgs& r, const PermuteArgs& p, cudaStream_t stream);
 void launch_route_only(const RouteArgs& r, cudaStream_t stream);
 void launch_gather_rows(const GatherArgs& a, int T, cudaStream_t stream);
-// gemm_id 1 or 2; n_tile in {16, 32, 64, 128} (GEMM1 also 256).  Returns a cudaError_t as int.
+// gemm_id 1 or 2; n_tile in {16, 32, 64, 128}.  Returns a cudaError_t as int.
 int launch_grouped_gemm(int gemm_id, int n_tile, const CUtensorMap& tm_w, const CUtensorMap& tm_b, const GemmArgs& a,
                         int ctas, cudaStream_t stream);
 constexpr int kFusedMaxTokens = 16;
@@ -136,6 +141,15 @@ int launch_decode(const CUtensorMap& tm_w1, const CUtensorMap& tm_x, const CUten
 int decode_kernel_init();
 int grouped_gemm_kblocks_per_stage(int gemm_id, int n_tile);   // K-blocks one TMA box of that kernel brings
 int grouped_gemm_init();   // one-time function attributes (dynamic shared memory opt-in)
+// Large batches (128-token tiles): GEMM1 with SwiGLU and the e4m3 plane split in its epilogue; GEMM2 storing fp32 rows
+// for the deterministic combine kernel, or (fused_combine) adding weighted rows into acc32 with a last-arriver bf16 cast.
+int grouped_gemm_large_init();
+int launch_grouped_gemm_large(int gemm_id, bool fused_combine, const CUtensorMap& tm_w, const CUtensorMap& tm_b,
+                              const GemmArgs& a, int ctas, cudaStream_t stream);
+// Zeroes `acc_floats` floats at acc32 (the accumulator and the counters behind it) and writes zero output rows for
+// tokens without a local expert.
+int launch_combine_prepare(float* acc32, size_t acc_floats, const uint32_t* local_mask, int T, uint16_t* out_bf16,
+                           uint16_t* const* out_rows, cudaStream_t stream);
 void launch_swiglu_split(const SwigluArgs& a, int T, cudaStream_t stream);
 void launch_combine(const CombineArgs& a, cudaStream_t stream);
 

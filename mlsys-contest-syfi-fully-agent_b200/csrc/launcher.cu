@@ -25,6 +25,7 @@ thread_local int g_last_cuda_error = 0;
 constexpr int kStages = 6;   // route+permute, gather, GEMM1, SwiGLU split, GEMM2, combine
 std::atomic<long long> g_launches{0};
 std::atomic<int> g_profiling{0};
+std::atomic<unsigned> g_options{0};
 struct StageEvents {
   cudaEvent_t ev[kStages + 1];
   bool created = false;
@@ -123,6 +124,7 @@ int ensure_device(DeviceState** out) {
     if (fn == nullptr || qres != cudaDriverEntryPointSuccess) return MOE_B200_EDEVICE;
     d.encode = reinterpret_cast<EncodeFn>(fn);
     int rc = grouped_gemm_init();
+    if (rc == 0) rc = grouped_gemm_large_init();
     if (rc == 0) rc = decode_kernel_init();
     if (rc != 0) {
       g_last_cuda_error = rc;
@@ -187,28 +189,13 @@ MapKey planes_map(const void* ptr, uint64_t rows, uint32_t box_rows, uint32_t kp
   return k;
 }
 
+// Token-tile width, chosen from T alone (no device read-back).  The tile is chosen for the rows an expert
+// typically gets (T / 32 with balanced routing), not for the worst case: an expert with more rows simply takes
+// several tiles.  Measured on balanced batches: 32-token tiles win up to T = 256, 64-token tiles up to T = 1024,
+// 128-token tiles beyond; 33..64 tokens keep 64-token tiles, which also serve small batches that pile onto a
+// few experts.
 int pick_n_tile(int T) {
-  static const int forced = [] {
-    const char* s = std::getenv("MOE_B200_NTILE");
-    return s ? std::atoi(s) : 0;
-  }();
-  if (forced == 16 || forced == 32 || forced == 64 || forced == 128 || forced == 256) return forced;
-  // 256-token tiles (GEMM1 only) exist for experiments (MOE_B200_NTILE=256); with eight promotion warps
-  // they are slower than 128-token tiles (the read-back of 256 TMEM columns per K-block dominates).
-  // The tile is chosen for the rows an expert typically gets (T / 32 with balanced routing), not for the worst
-  // case: an expert with more rows simply takes several tiles.  Measured on balanced batches: 32-token tiles
-  // win up to T = 256, 64-token tiles up to T = 1024, 128-token tiles beyond; 33..64 tokens keep 64-token
-  // tiles, which also serve small batches that pile onto a few experts.
   return T <= 16 ? 16 : T <= 32 ? 32 : T <= 64 ? 64 : T <= 256 ? 32 : T <= 1024 ? 64 : 128;
-}
-
-// Decode path selection (MOE_B200_FUSED_DECODE): 1 = one launch (default), 0 = the general multi-kernel path.
-int fused_decode_mode() {
-  static const int mode = [] {
-    const char* s = std::getenv("MOE_B200_FUSED_DECODE");
-    return s ? std::atoi(s) : 1;
-  }();
-  return mode;
 }
 
 bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
@@ -254,6 +241,8 @@ extern "C" int moe_fp8_block_scale_layout(int T, moe_b200_layout* out) {
   out->cq = L.cq;
   out->c_scale = L.c_scale;
   out->o = L.o;
+  out->acc32 = L.acc32;
+  out->tile_cnt = L.tile_cnt;
   out->total = moe_fp8_block_scale_workspace_bytes(T);
   return MOE_B200_OK;
 }
@@ -268,10 +257,11 @@ static int run_impl(const float* routing_logits, const uint16_t* routing_bias, c
   if (!routing_logits || !routing_bias || !hidden_states || !hidden_states_scale || !gemm1_weights ||
       !gemm1_weights_scale || !gemm2_weights || !gemm2_weights_scale || (!output && !output_rows) || !workspace)
     return MOE_B200_EINVAL;
-  // vector loads and TMA: 16 bytes for the logits, the fp8 tensors and the output; natural alignment for the rest
+  // vector loads and TMA: 16 bytes for the logits, the fp8 tensors, the weight scales and the output; natural
+  // alignment for the rest
   if (!aligned16(routing_logits) || !aligned16(hidden_states) || !aligned16(gemm1_weights) || !aligned16(gemm2_weights) ||
-      !aligned16(output) || !aligned2(routing_bias) || !aligned4(hidden_states_scale) || !aligned4(gemm1_weights_scale) ||
-      !aligned4(gemm2_weights_scale) || (reinterpret_cast<uintptr_t>(workspace) & 1023u) != 0)
+      !aligned16(output) || !aligned2(routing_bias) || !aligned4(hidden_states_scale) || !aligned16(gemm1_weights_scale) ||
+      !aligned16(gemm2_weights_scale) || (reinterpret_cast<uintptr_t>(workspace) & 1023u) != 0)
     return MOE_B200_EINVAL;
   if (workspace_bytes < moe_fp8_block_scale_workspace_bytes(T)) return MOE_B200_EWORKSPACE;
   DeviceState* dev = nullptr;
@@ -295,6 +285,12 @@ static int run_impl(const float* routing_logits, const uint16_t* routing_bias, c
   uint8_t* cq = ws + L.cq;
   float* c_scale = reinterpret_cast<float*>(ws + L.c_scale);
   float* o = reinterpret_cast<float*>(ws + L.o);
+  float* acc32 = reinterpret_cast<float*>(ws + L.acc32);
+  int* tile_cnt = reinterpret_cast<int*>(ws + L.tile_cnt);
+  const unsigned opts = g_options.load(std::memory_order_relaxed);
+  // more than 1024 tokens: 128-token tiles, SwiGLU in GEMM1's epilogue, optionally the combine in GEMM2's
+  const bool large = T > 1024 && !(opts & MOE_B200_OPT_UNFUSED);
+  const bool fast_combine = large && (opts & MOE_B200_OPT_FAST_COMBINE);
 
   const int n_tile = pick_n_tile(T);
   const int n_tile2 = n_tile > 128 ? 128 : n_tile;   // GEMM2's three-plane token operand does not fit 256-token stages
@@ -302,14 +298,15 @@ static int run_impl(const float* routing_logits, const uint16_t* routing_bias, c
 
   CUtensorMap tm_w13, tm_w2, tm_a, tm_c;
   const uint32_t kps1 = grouped_gemm_kblocks_per_stage(1, n_tile), kps2 = grouped_gemm_kblocks_per_stage(2, n_tile2);
-  if ((rc = get_map(dev, kblock_map(gemm1_weights, static_cast<uint64_t>(kELocal) * k2I, kH, 128, kps1), &tm_w13)))
+  // (the large-batch kernels take one K-block per box)
+  if ((rc = get_map(dev, kblock_map(gemm1_weights, static_cast<uint64_t>(kELocal) * k2I, kH, 128, large ? 1 : kps1), &tm_w13)))
     return rc;
   if ((rc = get_map(dev, kblock_map(gemm2_weights, static_cast<uint64_t>(kELocal) * kH, kI, 128, kps2), &tm_w2)))
     return rc;
-  if ((rc = get_map(dev, kblock_map(a_packed, L.rows_cap, kH, n_tile, kps1), &tm_a))) return rc;
+  if ((rc = get_map(dev, kblock_map(a_packed, L.rows_cap, kH, n_tile, large ? 1 : kps1), &tm_a))) return rc;
   if ((rc = get_map(dev, planes_map(cq, L.rows_cap, n_tile2, kps2), &tm_c))) return rc;
 
-  if (T <= kFusedMaxTokens && fused_decode_mode() != 0) {
+  if (T <= kFusedMaxTokens) {
     // Decode path: one launch.  The kernel routes, reads the token rows straight from hidden_states (all
     // tokens are one token tile), and runs both GEMMs with the SwiGLU and combine phases in between and after.
     static std::atomic<unsigned int> call_counter{0x9E3779B1u};
@@ -338,7 +335,7 @@ static int run_impl(const float* routing_logits, const uint16_t* routing_bias, c
   RouteArgs ra{routing_logits, routing_bias, T, local_expert_offset, routed_scaling_factor, topk_idx, topk_w,
                local_mask};
   PermuteArgs pa{T, local_expert_offset, n_tile, n_tile2, ctas, static_cast<int>(kps1), static_cast<int>(kps2), L.rows_cap, L.slab_rows, local_mask, topk_idx, topk_w,
-                 sched, perm_token, perm_weight, tok_rows, chunk_base};
+                 sched, perm_token, perm_weight, tok_rows, chunk_base, fast_combine ? 2 : large ? 1 : 0};
   stage_mark(0, stream);
   launch_route_permute(ra, pa, stream);
   MOE_CUDA(cudaGetLastError());
@@ -353,32 +350,65 @@ static int run_impl(const float* routing_logits, const uint16_t* routing_bias, c
 
   GemmArgs g1a{};
   g1a.sched = sched; g1a.w_scale = gemm1_weights_scale; g1a.b_scale = a_scale_rows; g1a.out = g1;
-  if ((rc = launch_grouped_gemm(1, n_tile, tm_w13, tm_a, g1a, ctas, stream))) {
-    g_last_cuda_error = rc;
-    return MOE_B200_ECUDA;
-  }
-  g_launches += 1;
-  stage_mark(3, stream);
-
-  SwigluArgs sa{sched, g1, cq, c_scale, L.rows_cap};
-  launch_swiglu_split(sa, T, stream);
-  MOE_CUDA(cudaGetLastError());
-  g_launches += 1;
-  stage_mark(4, stream);
-
+  g1a.rows_cap = L.rows_cap; g1a.cq = cq; g1a.c_scale = c_scale;
   GemmArgs g2a{};
   g2a.sched = sched; g2a.w_scale = gemm2_weights_scale; g2a.b_scale = c_scale; g2a.out = o;
-  if ((rc = launch_grouped_gemm(2, n_tile2, tm_w2, tm_c, g2a, ctas, stream))) {
-    g_last_cuda_error = rc;
-    return MOE_B200_ECUDA;
-  }
-  g_launches += 1;
-  stage_mark(5, stream);
+  g2a.rows_cap = L.rows_cap; g2a.perm_token = perm_token; g2a.perm_weight = perm_weight; g2a.local_mask = local_mask;
+  g2a.acc32 = acc32; g2a.tile_cnt = tile_cnt; g2a.out_bf16 = output; g2a.out_rows = output_rows;
 
-  CombineArgs ca{sched, o, local_mask, tok_rows, perm_weight, output, T, output_rows};
-  launch_combine(ca, stream);
-  MOE_CUDA(cudaGetLastError());
-  g_launches += 1;
+  if (large) {
+    if (fast_combine) {
+      // accumulator + counters are one span of the workspace
+      const size_t span = (L.tile_cnt - L.acc32) + static_cast<size_t>(T) * kMT2 * 4;
+      if ((rc = launch_combine_prepare(acc32, span / 4, local_mask, T, output, output_rows, stream))) {
+        g_last_cuda_error = rc;
+        return MOE_B200_ECUDA;
+      }
+      g_launches += 1;
+    }
+    if ((rc = launch_grouped_gemm_large(1, false, tm_w13, tm_a, g1a, ctas, stream))) {
+      g_last_cuda_error = rc;
+      return MOE_B200_ECUDA;
+    }
+    g_launches += 1;
+    stage_mark(3, stream);
+    stage_mark(4, stream);      // no SwiGLU kernel on this path
+    // GEMM2: the 16-warp kernel only for the fused combine; for fp32 rows the eight-warp kernel measures faster
+    if ((rc = fast_combine ? launch_grouped_gemm_large(2, true, tm_w2, tm_c, g2a, ctas, stream)
+                           : launch_grouped_gemm(2, n_tile2, tm_w2, tm_c, g2a, ctas, stream))) {
+      g_last_cuda_error = rc;
+      return MOE_B200_ECUDA;
+    }
+    g_launches += 1;
+    stage_mark(5, stream);
+  } else {
+    if ((rc = launch_grouped_gemm(1, n_tile, tm_w13, tm_a, g1a, ctas, stream))) {
+      g_last_cuda_error = rc;
+      return MOE_B200_ECUDA;
+    }
+    g_launches += 1;
+    stage_mark(3, stream);
+
+    SwigluArgs sa{sched, g1, cq, c_scale, L.rows_cap};
+    launch_swiglu_split(sa, T, stream);
+    MOE_CUDA(cudaGetLastError());
+    g_launches += 1;
+    stage_mark(4, stream);
+
+    if ((rc = launch_grouped_gemm(2, n_tile2, tm_w2, tm_c, g2a, ctas, stream))) {
+      g_last_cuda_error = rc;
+      return MOE_B200_ECUDA;
+    }
+    g_launches += 1;
+    stage_mark(5, stream);
+  }
+
+  if (!fast_combine) {
+    CombineArgs ca{sched, o, local_mask, tok_rows, perm_weight, output, T, output_rows};
+    launch_combine(ca, stream);
+    MOE_CUDA(cudaGetLastError());
+    g_launches += 1;
+  }
   stage_mark(6, stream);
   return MOE_B200_OK;
 }
@@ -510,6 +540,14 @@ extern "C" int moe_fp8_block_scale_status(const void* workspace, void* stream_v,
 }
 
 extern "C" long long moe_fp8_block_scale_launch_count(void) { return g_launches.load(); }
+
+extern "C" int moe_fp8_block_scale_set_options(unsigned int options) {
+  if (options & ~(MOE_B200_OPT_FAST_COMBINE | MOE_B200_OPT_UNFUSED)) return MOE_B200_EINVAL;
+  g_options.store(options);
+  return MOE_B200_OK;
+}
+
+extern "C" unsigned int moe_fp8_block_scale_get_options(void) { return g_options.load(); }
 
 extern "C" int moe_fp8_block_scale_set_profiling(int enable) {
   g_profiling.store(enable ? 1 : 0);

@@ -64,6 +64,7 @@ struct WorkspaceLayout {
   int slab_rows;       // rows of the fp32 slab areas: max(rows_cap, kMinSlabRows)
   size_t sched, topk_idx, topk_w, local_mask, perm_token, perm_weight, tok_rows, chunk_base;
   size_t a_packed, a_scale_rows, g1, cq, c_scale, o;
+  size_t acc32, tile_cnt;   // fused combine of the large-batch GEMM2: fp32 output accumulator and arrival counters
   size_t total;
 };
 
@@ -96,6 +97,8 @@ inline WorkspaceLayout make_layout(int T) {
   L.cq = take(static_cast<size_t>(kNTerms) * L.rows_cap * kI);
   L.c_scale = take(static_cast<size_t>(L.rows_cap) * kKB2 * 4);
   L.o = take(static_cast<size_t>(L.slab_rows) * kH * 4);
+  L.acc32 = take(Tz * kH * 4);
+  L.tile_cnt = take(Tz * kMT2 * 4);
   L.total = off;
   return L;
 }

@@ -134,8 +134,10 @@ __device__ void permute_block(const PermuteArgs& a) {
     const int n_sel = __shfl_sync(0xFFFFFFFFu, inc, 31), tiles_total = __shfl_sync(0xFFFFFFFFu, tinc, 31);
     const int tiles_total2 = __shfl_sync(0xFFFFFFFFu, tinc2, 31);
     const int n_sel_pad = (n_sel + 15) & ~15;
-    const int s1 = choose_split_warp(tiles_total * kMT1, kMaxSplit1, a.ctas, n_sel_pad, a.slab_rows, lane, kKB1, a.kps1);
-    const int s2 = choose_split_warp(tiles_total2 * kMT2, kMaxSplit2, a.ctas, n_sel_pad, a.slab_rows, lane, kKB2, a.kps2);
+    int s1 = choose_split_warp(tiles_total * kMT1, kMaxSplit1, a.ctas, n_sel_pad, a.slab_rows, lane, kKB1, a.kps1);
+    int s2 = choose_split_warp(tiles_total2 * kMT2, kMaxSplit2, a.ctas, n_sel_pad, a.slab_rows, lane, kKB2, a.kps2);
+    if (a.large) s1 = 1;          // the SwiGLU epilogue needs whole K sums
+    if (a.large > 1) s2 = 1;      // ... and so does the fused combine
     if (lane == 31) {
       sc->offs[0] = 0;
       sc->tile_prefix[0] = 0;
@@ -150,7 +152,7 @@ __device__ void permute_block(const PermuteArgs& a) {
       sc->tiles_total = tiles_total;
       sc->split1 = s1;
       sc->split2 = s2;
-      sc->items1 = tiles_total * kMT1 * s1;
+      sc->items1 = a.large ? tiles_total * kKB2 : tiles_total * kMT1 * s1;   // large: one item per 128-column block of C
       sc->items2 = tiles_total2 * kMT2 * s2;
     }
   }

@@ -30,6 +30,8 @@ EXPORTS = [
     "moe_fp8_block_scale_route",
     "moe_fp8_block_scale_quantize_activations",
     "moe_fp8_block_scale_run_rows",
+    "moe_fp8_block_scale_set_options",
+    "moe_fp8_block_scale_get_options",
     "moe_ep_dispatch_push",
     "moe_ep_sum_shards",
 ]
@@ -42,7 +44,7 @@ class Layout(ctypes.Structure):
                 ("n_terms", ctypes.c_int32)] + \
                [(n, ctypes.c_uint64) for n in ("sched", "topk_idx", "topk_w", "local_mask", "perm_token",
                                                "perm_weight", "tok_rows", "a_packed", "a_scale_rows", "g1", "cq", "c_scale", "o",
-                                               "total")]
+                                               "acc32", "tile_cnt", "total")]
 
 
 class Sched(ctypes.Structure):
@@ -97,6 +99,10 @@ def _load() -> ctypes.CDLL:
     lib.moe_ep_dispatch_push.argtypes = [vp, vp, vp, i32, vp, i32, ctypes.POINTER(EpSegment), i32, vp]
     lib.moe_ep_sum_shards.restype = i32
     lib.moe_ep_sum_shards.argtypes = [vp, vp, i32, vp, vp]
+    lib.moe_fp8_block_scale_set_options.restype = i32
+    lib.moe_fp8_block_scale_set_options.argtypes = [ctypes.c_uint]
+    lib.moe_fp8_block_scale_get_options.restype = ctypes.c_uint
+    lib.moe_fp8_block_scale_get_options.argtypes = []
     lib.moe_fp8_block_scale_launch_count.restype = ctypes.c_longlong
     lib.moe_fp8_block_scale_launch_count.argtypes = []
     lib.moe_fp8_block_scale_set_profiling.restype = i32
@@ -107,6 +113,18 @@ def _load() -> ctypes.CDLL:
 
 
 lib = _load()
+
+
+OPT_FAST_COMBINE, OPT_UNFUSED = 1, 2
+
+
+def set_options(options: int):
+    """Process-wide operator options (include/moe_b200.h: MOE_B200_OPT_*)."""
+    check(lib.moe_fp8_block_scale_set_options(int(options)))
+
+
+def get_options() -> int:
+    return int(lib.moe_fp8_block_scale_get_options())
 
 
 def launch_count() -> int:

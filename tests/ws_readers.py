@@ -69,3 +69,17 @@ def intermediates(pkg, T: int, workspace=None, device=None, stages: bool = True)
         out["c"] = c.view(n_sel, I).cpu()
         out["a_packed"] = arr(L.a_packed, n_sel * H, torch.uint8, (n_sel, H)).cpu()
     return out
+
+
+def swiglu_planes(pkg, T: int, workspace=None, device=None):
+    """The SwiGLU output as GEMM2 reads it, left by the last call with ``T`` tokens: (planes u8 [3, n_sel, 2048],
+    scales f32 [n_sel, 16]) on the device."""
+    op, loader = pkg.op, pkg.loader
+    dev = torch.device(device if device is not None else "cuda")
+    ws = workspace or op._default_workspace(dev)
+    torch.cuda.synchronize(ws.device)
+    L = loader.layout(T)
+    n_sel = op.read_schedule(T, workspace, device).n_sel
+    cq = ws.view(L.cq, L.n_terms * L.rows_cap * I).view(L.n_terms, L.rows_cap, I)[:, :n_sel].clone()
+    cs = ws.view(L.c_scale, L.rows_cap * 16 * 4).view(torch.float32).view(L.rows_cap, 16)[:n_sel].clone()
+    return cq, cs
