@@ -31,15 +31,6 @@
 // bounded; a timeout raises the CTA's abort flag, all roles leave through the normal teardown, and an
 // error bit is left in the schedule block.
 #include "ptx.cuh"
-#ifdef MOE_TRACE
-// Debug build only: time stamps (ns) of every CTA, [cta][role][slot].
-namespace moe { __device__ unsigned long long g_moe_dtrace[148][4][16]; }
-#define DTRACE(role, slot) do { if (blockIdx.x < 148) moe::g_moe_dtrace[blockIdx.x][role][slot] = moe::globaltimer_ns(); } while (0)
-#define MOE_ROUTE_TRACE(slot) DTRACE(3, slot)
-#define MOE_ROUTE_CLK(slot) do { if (blockIdx.x < 148) moe::g_moe_dtrace[blockIdx.x][0][slot] = clock64(); } while (0)
-#else
-#define DTRACE(role, slot) do { } while (0)
-#endif
 #include "epilogue_device.cuh"
 #include "gemm_common.cuh"
 
@@ -150,14 +141,7 @@ __device__ __forceinline__ bool issue_items(int tiles, const Aux* aux, uint32_t 
     for (int kb = w.kb0; kb < w.kb1; kb += DC::KPS) {
       if (!mbar_wait(tempty_base + r.buf * 8, r.bph ^ 1u, abort_flag)) return false;
       if (!mbar_wait(full_base + r.stage * 8, r.ph, abort_flag)) return false;
-#ifdef MOE_TRACE
-      if (GEMM == 2 && first && kb < w.kb0 + 4 * DC::KPS) DTRACE(0, 4 + (kb - w.kb0) / DC::KPS);
-#endif
       tc_fence_after_sync();
-#ifdef MOE_TRACE
-      const bool tr = GEMM == 2 && first && kb == w.kb0 + 2 * DC::KPS;
-      if (tr) moe::g_moe_dtrace[blockIdx.x][3][8] = clock64();
-#endif
       const uint32_t sbase = smem_base + r.stage * DC::STAGE_BYTES;
 #pragma unroll
       for (int u = 0; u < DC::KPS; ++u) {
@@ -167,16 +151,7 @@ __device__ __forceinline__ bool issue_items(int tiles, const Aux* aux, uint32_t 
 #pragma unroll
         for (int k4 = 0; k4 < 4; ++k4) umma_f8(d, adesc + 2 * k4, bdesc + 2 * k4, idesc, k4 != 0 ? 1u : 0u);
       }
-#ifdef MOE_TRACE
-      if (tr) moe::g_moe_dtrace[blockIdx.x][3][9] = clock64();
-#endif
       umma_commit(done_base + r.stage * 8);
-#ifdef MOE_TRACE
-      if (tr) moe::g_moe_dtrace[blockIdx.x][3][10] = clock64();
-#endif
-      if (GEMM == 2 && first && kb == w.kb0) DTRACE(1, 4);
-      if (GEMM == 2 && first && kb == w.kb0 + 3 * DC::KPS) DTRACE(1, 5);
-      if (GEMM == 2) DTRACE(1, 6);
       r.advance();
     }
   }
@@ -265,7 +240,6 @@ __device__ __forceinline__ void promote_items(const DecodeArgs& a, EpiCtx& c, in
     const bool have_next = part.next(c.aux, wn);
     c.sync();   // this piece's table is complete and the other one is free
     if (!c.ok) break;
-    if (GEMM == 2 && nitem == 0 && c.etid == 0) DTRACE(2, 6);
     if (have_next) {
 #pragma unroll
       for (int x = 0; x < kMaxE; ++x) pre[x] = scale_product<GEMM>(a, c.fa, wn, c.etid + x * kEpiThreads);
@@ -275,7 +249,6 @@ __device__ __forceinline__ void promote_items(const DecodeArgs& a, EpiCtx& c, in
     for (int j = 0; j < CPW; ++j) acc[j] = 0.0f;
     for (int kbl = 0; kbl < nkb; kbl += DC::KPS) {
       if (!mbar_wait(done_base + c.r.stage * 8, c.r.ph, c.abort_flag)) { c.ok = false; break; }
-      if (GEMM == 2 && nitem == 0 && kbl == 0 && c.etid == 0) DTRACE(2, 7);
       tc_fence_after_sync();
       const uint32_t taddr = c.tmem_base + lane_addr + c.r.buf * DC::BUF_COLS + c.h * CPW;
       float v[DC::KPS][PLANES][CPW];
@@ -350,7 +323,6 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_w1, const __grid_constant__
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  if (threadIdx.x == 0) DTRACE(0, 0);
   griddep_launch_dependents();
   MoeSched* sched = a.g.sched;
   // everything that does not depend on earlier work in the stream first: barriers, descriptors, TMEM
@@ -373,7 +345,6 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_w1, const __grid_constant__
     tmem_relinquish();
   }
   griddep_wait();   // the workspace and the output belong to earlier launches until here
-  if (threadIdx.x == 0) DTRACE(0, 1);
   unsigned int* bar = sched->bar1;
   if (blockIdx.x == 0 && threadIdx.x == 0) grid_barrier_init(bar, a.g.call_tag);
   decode_route_schedule(a.g, smem, aux, fa, sched);
@@ -385,7 +356,6 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_w1, const __grid_constant__
   const uint32_t tmem_base = aux->tmem_base;
   volatile int* abort_flag = &aux->abort;
   const unsigned int n_ctas = gridDim.x;
-  if (threadIdx.x == 0) DTRACE(0, 2);
 
   if (warp < kFirstEpiWarp) {
     setmaxnreg_dec<kRegsControl>();
@@ -413,7 +383,6 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_w1, const __grid_constant__
             }
           }
         }
-        DTRACE(1, 0);
         // GEMM2: the weight box of a stage is requested as soon as the stage is free, up to a full ring
         // ahead of the token-operand boxes, which wait for the planes (grid barrier 2).
         Part<2> wpart, bpart;
@@ -427,7 +396,6 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_w1, const __grid_constant__
         while (ok && bhave) {
           if (ready ? ahead > 0 : (ahead == DC::STAGES || !whave)) {
             if (!ready) {
-              DTRACE(1, 1);
               // The ring is full of GEMM2 weights and HBM would now idle until the planes exist (two grid
               // barriers and the SwiGLU phase away): ask for the weight boxes behind the ring into L2, so that
               // after the barrier they arrive at L2 latency.  Bounded so that the slabs and planes stay in L2 too.
@@ -448,7 +416,6 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_w1, const __grid_constant__
               if (!grid_barrier_wait(bar, a.g.call_tag, 2 * n_ctas)) { *abort_flag = 1; ok = false; break; }
               fence_proxy_async_global();   // the planes were written with ordinary stores by other SMs
               ready = true;
-              DTRACE(1, 2);
             }
             tma_load_4d(smem_base + bstage * DC::STAGE_BYTES + DC::B_OFF, &tm_c, 0, bw.row0, 0, bkb,
                         full_base + bstage * 8);                     // [2 K-blocks][3 planes][16 rows][128 B]
@@ -473,7 +440,6 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_w1, const __grid_constant__
             }
           }
         }
-        DTRACE(1, 3);
       }
       __syncwarp();   // block-wide barriers below need whole warps
     } else if (warp == 1) {
@@ -504,7 +470,6 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_w1, const __grid_constant__
     if (c.etid == 0 && !grid_barrier_tag_wait(bar, a.g.call_tag)) *abort_flag = 1;
 
     promote_items<1>(a, c, tiles, n_sel_pad, 0.0f);
-    if (c.etid == 0) DTRACE(2, 0);
 
     // first GEMM2 item: the weight-scale factor of this thread's table entry does not depend on GEMM1;
     // fetching it here takes its DRAM latency off the path between grid barrier 2 and the first promotion
@@ -528,7 +493,6 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_w1, const __grid_constant__
       if (!grid_barrier_wait(bar, a.g.call_tag, n_ctas)) *abort_flag = 1;
     }
     c.sync();
-    if (c.etid == 0) DTRACE(2, 1);
     if (c.ok && !*abort_flag) {
       // SwiGLU + split of this CTA's share of the (row, K-block) units.  Up to 15 rows after the last one
       // are zero-filled: the 16-row token boxes of GEMM2 read them, and rows nobody has written would come
@@ -558,20 +522,15 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_w1, const __grid_constant__
       }
     }
     // grid barrier 2: the planes and their scales are complete (the producers' TMA loads read them)
-    if (c.etid == 0) DTRACE(3, 3);
     fence_proxy_async_global();
-    if (c.etid == 0) DTRACE(3, 4);
     c.sync();
-    if (c.etid == 0) DTRACE(3, 5);
     if (c.ok && c.etid == 0) {
       grid_barrier_arrive(bar);
       if (!grid_barrier_wait(bar, a.g.call_tag, 2 * n_ctas)) *abort_flag = 1;
     }
     c.sync();
-    if (c.etid == 0) DTRACE(2, 2);
 
     if (c.ok && !*abort_flag) promote_items<2>(a, c, tiles, n_sel_pad, ws2_first);
-    if (c.etid == 0) DTRACE(2, 3);
 
     // grid barrier 3: every GEMM2 slab is complete
     c.sync();
@@ -580,7 +539,6 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_w1, const __grid_constant__
       if (!grid_barrier_wait(bar, a.g.call_tag, 3 * n_ctas)) *abort_flag = 1;
     }
     c.sync();
-    if (c.etid == 0) DTRACE(2, 4);
     if (c.ok && !*abort_flag) {
       constexpr int kVec = kH / 4;
       constexpr int U2 = Part<2>::U;
@@ -601,7 +559,6 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_w1, const __grid_constant__
                      a.g.out_rows ? a.g.out_rows[t] : a.g.out_bf16 + static_cast<size_t>(t) * kH);
       }
     }
-    if (c.etid == 0) DTRACE(2, 5);
   }
 
   tc_fence_before_sync();
@@ -612,16 +569,10 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_w1, const __grid_constant__
     tc_fence_after_sync();
     tmem_dealloc(tmem_base, DC::TMEM_COLS);
   }
-  if (threadIdx.x == 0) DTRACE(0, 3);
 }
 
 }  // namespace
 
-#ifdef MOE_TRACE
-extern "C" int moe_debug_dtrace(unsigned long long* host, int bytes) {
-  return static_cast<int>(cudaMemcpyFromSymbol(host, g_moe_dtrace, bytes));
-}
-#endif
 
 int decode_kernel_init() {
   return static_cast<int>(cudaFuncSetAttribute(decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, DC::SMEM_BYTES));

@@ -5,13 +5,6 @@
 #include "ptx.cuh"
 #include "route_device.cuh"
 
-#ifndef MOE_ROUTE_CLK
-#define MOE_ROUTE_CLK(slot) do { } while (0)
-#endif
-#ifndef MOE_ROUTE_TRACE
-#define MOE_ROUTE_TRACE(slot) do { } while (0)   // debug builds of an including file may stamp the routing phases
-#endif
-
 namespace moe {
 
 // Three warpgroups: warpgroup 0 holds the TMA producer (warp 0) and the UMMA issuer (warp 1) and gives
@@ -163,7 +156,6 @@ __device__ __forceinline__ void decode_route_schedule(const GemmArgs& a, uint8_t
       for (int t = 0; t < kBlockRouteMaxTokens; ++t)                 // all tokens' logits in flight
         x[t] = t < a.T ? a.logits[static_cast<size_t>(t) * kEGlobal + e] : 0.0f;
       const float bias_e = __uint_as_float(static_cast<uint32_t>(a.bias_bf16[e]) << 16);
-      if (threadIdx.x == 0) MOE_ROUTE_TRACE(0);
 #pragma unroll 1
       for (int t = 0; t < a.T; ++t) {
         float xt = x[0];
@@ -226,7 +218,6 @@ __device__ __forceinline__ void decode_route_schedule(const GemmArgs& a, uint8_t
         // warp 0 has read selidx / sels before it reaches that barrier
       }
     }
-    if (threadIdx.x == 0) MOE_ROUTE_TRACE(1);
   } else {
   float* bias_s = fa->sval;
   for (int i = threadIdx.x; i < kEGlobal; i += kGemmThreads)
@@ -247,13 +238,11 @@ __device__ __forceinline__ void decode_route_schedule(const GemmArgs& a, uint8_t
     }
   }
   __syncthreads();
-  if (threadIdx.x == 0) MOE_ROUTE_TRACE(0);
   // Both tokens of a warp go through every step together (b = 0, 1): the steps of one token are a chain of
   // dependent operations, those of two tokens are independent and overlap.  `on[b]` is uniform over the warp.
   if (warp < a.T) {
     const bool on[kTok] = {true, warp + kWarps < a.T};
     unsigned long long c[kTok][8];
-    if (threadIdx.x == 0) MOE_ROUTE_CLK(8);
 #pragma unroll
     for (int b = 0; b < kTok; ++b) {
       if (!on[b]) continue;
@@ -294,7 +283,6 @@ __device__ __forceinline__ void decode_route_schedule(const GemmArgs& a, uint8_t
       for (int i = 0; i < 8; ++i)
         c[b][i] = kept ? (static_cast<unsigned long long>(k[i]) << 32) | static_cast<unsigned int>(255 - (lane * 8 + i)) : 0ull;
     }
-    if (threadIdx.x == 0) MOE_ROUTE_CLK(9);
 #define MOE_CX(p, q)                                               \
     {                                                              \
       const unsigned long long hi = max(c[b][p], c[b][q]);         \
@@ -312,7 +300,6 @@ __device__ __forceinline__ void decode_route_schedule(const GemmArgs& a, uint8_t
       MOE_CX(2, 4) MOE_CX(3, 5)
       MOE_CX(3, 4)
     }
-    if (threadIdx.x == 0) MOE_ROUTE_CLK(10);
 #pragma unroll
     for (int d = 1; d < 32; d <<= 1) {                             // butterfly merge over the warp
 #pragma unroll
@@ -329,7 +316,6 @@ __device__ __forceinline__ void decode_route_schedule(const GemmArgs& a, uint8_t
       }
     }
 #undef MOE_CX
-    if (threadIdx.x == 0) MOE_ROUTE_CLK(11);
     __syncwarp();                                                  // the warp's unbiased scores are in shared memory
 #pragma unroll
     for (int b = 0; b < kTok; ++b) {
@@ -355,9 +341,7 @@ __device__ __forceinline__ void decode_route_schedule(const GemmArgs& a, uint8_t
       bit = __reduce_or_sync(0xFFFFFFFFu, bit);
       if (lane == 0) fa->mask[t] = bit;
     }
-    if (threadIdx.x == 0) MOE_ROUTE_CLK(12);
   }
-  if (threadIdx.x == 0) MOE_ROUTE_TRACE(1);
   }   // T > kBlockRouteMaxTokens
   fence_proxy_async_smem();   // the logits scratch is about to be overwritten by TMA (async proxy)
   __syncthreads();
@@ -409,7 +393,6 @@ __device__ __forceinline__ void decode_route_schedule(const GemmArgs& a, uint8_t
       }
     }
   }
-  if (threadIdx.x == 0) MOE_ROUTE_TRACE(2);
   __syncthreads();
   if (warp == kFirstEpiWarp && lane < a.T) {   // lane = token: row lists and weights (CTA 0 also publishes them)
     const int t = lane;

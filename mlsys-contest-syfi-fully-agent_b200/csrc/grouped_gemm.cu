@@ -15,7 +15,7 @@
 //   warp 0  producer: TMA (SWIZZLE_128B, no multicast) of one weight tile
 //           [128 rows x 128 K-bytes] and the token tile(s) [N_TILE x 128] per K-block
 //           into a ring of STAGES shared-memory stages.
-//   warp 1  issuer: one thread issues the tcgen05.mma kind::f8f6f4 (M128, K32) of a
+//   warp 1 (and warp 2 from 32-token tiles up, alternate stages)  issuer: one thread issues the tcgen05.mma kind::f8f6f4 (M128, K32) of a
 //           K-block into its own TMEM columns.  For GEMM2 the kNTerms e4m3 planes of
 //           the token operand sit back to back in shared memory and, while they fit
 //           N <= 256, are consumed as ONE operand of N = kNTerms * N_TILE rows, so the
@@ -23,7 +23,7 @@
 //           G consecutive K-blocks form a hand-off group with one "full" barrier;
 //           NBUF groups rotate through TMEM so that the hand-off latency between the
 //           tensor core and the promotion warps is hidden.
-//   warps 2-9  promotion + epilogue (two warps per TMEM lane quarter, each owning half
+//   warps 4-11 promotion + epilogue (two warps per TMEM lane quarter, each owning half
 //           of the token columns): tcgen05.ld the partials of a group, release the TMEM
 //           buffer, multiply by w_scale[e, m, kb] * b_scale[row, kb] and accumulate in
 //           registers (the scales are arbitrary fp32 per 128-block, so they cannot ride
@@ -38,17 +38,6 @@
 #include "gemm_common.cuh"
 
 namespace moe {
-
-#ifdef MOE_TRACE
-// Debug build only: per-role time stamps of CTA 0, [gemm][role][slot].
-__device__ unsigned long long g_moe_trace[2][4][256];
-#define TRACE(role, slot) do { if (blockIdx.x == 0 && (slot) < 256) g_moe_trace[GEMM - 1][role][slot] = static_cast<unsigned long long>(clock64()); } while (0)
-// per-stage stamps of CTA 0 in steady state: stages 40..71 of the CTA, `per` stamps each
-#define TRACE_STAGE(role, n, per, j) do { if ((n) >= 40 && (n) < 72) TRACE(role, ((n) - 40) * (per) + (j)); } while (0)
-#else
-#define TRACE(role, slot) do { } while (0)
-#define TRACE_STAGE(role, n, per, j) do { } while (0)
-#endif
 
 namespace {
 
@@ -153,7 +142,6 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  if (threadIdx.x == 0) TRACE(3, 0);
   griddep_launch_dependents();
   MoeSched* sched = a.sched;
   // everything that does not depend on earlier kernels first: barriers, descriptors, TMEM
@@ -174,7 +162,6 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
     tmem_relinquish();
   }
   griddep_wait();   // the schedule, the operands and the output slabs belong to earlier kernels until here
-  if (threadIdx.x == 0) TRACE(3, 5);
   int items, split, n_sel_pad;
   items = GEMM == 1 ? sched->items1 : sched->items2;
   split = GEMM == 1 ? sched->split1 : sched->split2;
@@ -188,7 +175,6 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
   tc_fence_after_sync();
   const uint32_t tmem_base = aux->tmem_base;
   volatile int* abort_flag = &aux->abort;
-  if (threadIdx.x == 0) TRACE(3, 1);
 
   if (warp < kFirstEpiWarp) {
   setmaxnreg_dec<kRegsControl>();
@@ -199,15 +185,12 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
       const uint32_t full_base = smem_u32(&aux->full[0]), done_base = smem_u32(&aux->done[0]);
       uint32_t stage = 0, ph = 0;
       bool ok = true;
-      [[maybe_unused]] int nst = 0;
       for (int i = blockIdx.x; ok && i < items; i += gridDim.x) {
         const Item w = decode_item<GEMM, N_TILE>(i, split, aux);
         const int wy = w.e * C::M_TOTAL + w.m * 128;
         const int by = w.row0;
-        for (int kb = w.kb0; kb < w.kb1; kb += C::KPS, ++nst) {
-          TRACE_STAGE(0, nst, 2, 0);
+        for (int kb = w.kb0; kb < w.kb1; kb += C::KPS) {
           if (!mbar_wait(done_base + stage * 8, ph ^ 1u, abort_flag)) { ok = false; break; }
-          TRACE_STAGE(0, nst, 2, 1);
           const uint32_t bar = full_base + stage * 8;
           mbar_arrive_expect_tx(bar, C::STAGE_BYTES);
           const uint32_t dst = smem_base + stage * C::STAGE_BYTES;
@@ -242,11 +225,8 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
             if (++buf == C::NBUF) { buf = 0; bph ^= 1u; }
             continue;
           }
-          TRACE_STAGE(1, nst, 4, 0);
           if (!mbar_wait(tempty_base + buf * 8, bph ^ 1u, abort_flag)) { ok = false; break; }
-          TRACE_STAGE(1, nst, 4, 1);
           if (!mbar_wait(full_base + stage * 8, ph, abort_flag)) { ok = false; break; }
-          TRACE_STAGE(1, nst, 4, 2);
           tc_fence_after_sync();
           const uint32_t sbase = smem_base + stage * C::STAGE_BYTES;
 #pragma unroll
@@ -265,7 +245,6 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
             }
           }
           umma_commit(done_base + stage * 8);
-          TRACE_STAGE(1, nst, 4, 3);
           if (++stage == C::STAGES) { stage = 0; ph ^= 1u; }
           if (++buf == C::NBUF) { buf = 0; bph ^= 1u; }
         }
@@ -321,7 +300,6 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
     for (int i = blockIdx.x; ok && i < items; i += gridDim.x, ++nitem) {
       const Item w = decode_item<GEMM, N_TILE>(i, split, aux);
       const int nkb = w.kb1 - w.kb0;
-      if (etid == 0 && nitem < 16) TRACE(3, 32 + 4 * nitem);
       float* sc = sc_base + (C::SC_BUFS == 2 ? (nitem & 1u) * (C::KB * N_TILE) : 0);
       const int inext = i + gridDim.x;
       if (C::SC_BUFS == 1) {
@@ -344,7 +322,6 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
 #pragma unroll
         for (int x = 0; x < kMaxE; ++x) pre[x] = load_scale(wn, etid + x * kEpiThreads);
       }
-      if (etid == 0 && nitem < 16) TRACE(3, 33 + 4 * nitem);
 
       float acc[C::CPW];
 #pragma unroll
@@ -355,9 +332,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
         // lane = token row (row0 + 32 q + lane), columns = this warp's half of the 128 weight rows
         const int trow = q * 32 + lane;
         for (int kbl = 0; kbl < nkb; kbl += C::G, ++nst) {
-          if (etid == 0) TRACE_STAGE(2, nst, 4, 0);
           if (!mbar_wait(done_base + stage * 8, ph, abort_flag)) { ok = false; break; }
-          if (etid == 0) TRACE_STAGE(2, nst, 4, 1);
           tc_fence_after_sync();
           const uint32_t taddr = tmem_base + lane_addr + buf * (C::G * C::KB_COLS) + h * C::CPW;
 #pragma unroll
@@ -371,20 +346,16 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
               tc_fence_before_sync();
               __syncwarp();
               if (lane == 0) mbar_arrive(tempty_base + buf * 8);
-              if (etid == 0) TRACE_STAGE(2, nst, 4, 2);
             }
 #pragma unroll
             for (int j = 0; j < C::CPW; ++j) acc[j] = fmaf(v[j], f, acc[j]);
           }
-          if (etid == 0) TRACE_STAGE(2, nst, 4, 3);
           if (++stage == C::STAGES) { stage = 0; ph ^= 1u; }
           if (++buf == C::NBUF) { buf = 0; bph ^= 1u; }
         }
       } else
       for (int kbl = 0; kbl < nkb; kbl += C::G, ++nst) {
-        if (etid == 0) TRACE_STAGE(2, nst, 4, 0);
         if (!mbar_wait(done_base + stage * 8, ph, abort_flag)) { ok = false; break; }
-        if (etid == 0) TRACE_STAGE(2, nst, 4, 1);
         tc_fence_after_sync();
         const uint32_t taddr = tmem_base + lane_addr + buf * (C::G * C::KB_COLS) + h * C::CPW;
 #pragma unroll
@@ -401,7 +372,6 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
               tc_fence_before_sync();
               __syncwarp();
               if (lane == 0) mbar_arrive(tempty_base + buf * 8);
-              if (etid == 0) TRACE_STAGE(2, nst, 4, 2);
             }
             const float4* scv = reinterpret_cast<const float4*>(sc + (kbl + g) * N_TILE + h * C::CPW + c0);
 #pragma unroll
@@ -422,12 +392,10 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
             }
           }
         }
-        if (etid == 0) TRACE_STAGE(2, nst, 4, 3);
         if (++stage == C::STAGES) { stage = 0; ph ^= 1u; }
         if (++buf == C::NBUF) { buf = 0; bph ^= 1u; }
       }
       if (!ok) break;
-      if (etid == 0 && nitem < 16) TRACE(3, 34 + 4 * nitem);
       if constexpr (C::TOK_ON_M) {
         if (q * 32 + lane < w.valid) {      // one token row, 64 consecutive outputs
           float* out = a.out + (static_cast<size_t>(w.s) * n_sel_pad + w.row0 + q * 32 + lane) * C::M_TOTAL + w.m * 128 + h * C::CPW;
@@ -454,9 +422,6 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
 
   tc_fence_before_sync();
   __syncthreads();
-  if (threadIdx.x == 0) TRACE(3, 2);
-  if (threadIdx.x == 64) TRACE(3, 9);
-  if (threadIdx.x == 32) TRACE(3, 10);
   if (threadIdx.x == 0 && aux->abort) atomicOr(&sched->status, GEMM == 1 ? kErrGemm1Timeout : kErrGemm2Timeout);
   if (warp == 1) {
     __syncwarp();
@@ -481,11 +446,6 @@ int init_one() {
 
 }  // namespace
 
-#ifdef MOE_TRACE
-extern "C" int moe_debug_trace(unsigned long long* host, int bytes) {
-  return static_cast<int>(cudaMemcpyFromSymbol(host, g_moe_trace, bytes));
-}
-#endif
 
 int grouped_gemm_kblocks_per_stage(int gemm_id, int n_tile) {
 #define MOE_CASE(G, N) \

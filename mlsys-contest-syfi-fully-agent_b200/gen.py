@@ -204,11 +204,4 @@ def digest(*tensors: torch.Tensor) -> str:
     return h.hexdigest()
 
 
-# Named workloads: the configurations the headline metric is quoted on.
-WORKLOADS = {
-    "cpu_ref_t8":   dict(T=8, seed=0, skew=False),
-    "decode_t1":    dict(T=1, seed=0, skew=False),
-    "skew_t64":     dict(T=64, seed=0, skew=True),
-    "prefill_t4096": dict(T=4096, seed=0, skew=False),
-}
 ROUTED_SCALING_FACTOR = 2.5

@@ -35,7 +35,10 @@ def test_static_routing_matches_workspace_entry_point(pkg):
     dev = torch.device("cuda", 0)
     W = pkg.gen.make_shard_weights(0, dev, experts=[])       # routing does not read the weights
     rsf = 2.5
-    batches = [(2500, 1, False, 32), (300, 0, True, 0), (37, 3, False, 64)]   # big first: later calls see leftovers
+    # big first: later calls see leftovers.  4096 is the entry point's limit (the whole fixed array), 32 and 1
+    # take the single-CTA routing + permutation launch.
+    batches = [(4096, 2, False, 0), (2500, 1, False, 32), (300, 0, True, 0), (37, 3, False, 64), (32, 6, True, 0),
+               (1, 3, False, 0)]
     tokens = [pkg.gen.make_tokens(T, seed, dev, skew) for T, seed, skew, _ in batches]
     got = [call_static(pkg, tok, T, off, rsf, dev) for tok, (T, _, _, off) in zip(tokens, batches)]
     for tok, (T, _, _, off), (idx, w, offs, ptok, pw) in zip(tokens, batches, got):
