@@ -206,7 +206,7 @@ bool aligned2(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 1u) == 0
 
 void set_last_cuda_error(int cuda_error) { g_last_cuda_error = cuda_error; }
 void count_launches(int n) { g_launches += n; }
-int route_permute_launches(int T) { return T <= 32 ? 1 : T <= 1024 ? 2 : 3; }
+int route_permute_launches(int T) { return T <= 32 ? 1 : T <= 1024 ? 2 : 4; }
 
 }  // namespace moe
 

@@ -85,7 +85,22 @@ __device__ __forceinline__ int fill_chunk(const PermuteArgs& a, int c, int base,
 // scan over (expert, warp) then gives every warp its first row for every expert, and phase
 // 2 fills rows in token order, so rows are ascending in token inside ascending expert.
 // Requires the routing outputs of all T tokens to be visible.
-__device__ void permute_block(const PermuteArgs& a) {
+// Tokens of chunk c (lane = token) per local expert: lane le returns the count of expert le.
+__device__ __forceinline__ int chunk_counts(const PermuteArgs& a, int c, int lane) {
+  const int t = c * 32 + lane;
+  const uint32_t m = t < a.T ? a.local_mask[t] : 0u;
+  int cnt = 0;
+#pragma unroll
+  for (int le = 0; le < kELocal; ++le) {
+    const int n = __popc(__ballot_sync(0xFFFFFFFFu, (m >> le) & 1u));
+    if (lane == le) cnt = n;
+  }
+  return cnt;
+}
+
+// `counted`: chunk_base already holds every chunk's per-expert counts (written by chunk_count_kernel, many
+// CTAs); otherwise this CTA counts the masks itself.
+__device__ void permute_block(const PermuteArgs& a, bool counted) {
   __shared__ int s_wcount[32][kELocal + 1];     // [warp][expert]: count, then first row (+1: no bank conflicts)
   const int lane = threadIdx.x & 31;
   const int warp = threadIdx.x >> 5;
@@ -95,15 +110,7 @@ __device__ void permute_block(const PermuteArgs& a) {
 
   // phase 1: lane le accumulates this warp's count for expert le
   int cnt = 0;
-  for (int c = c0; c < c1; ++c) {
-    const int t = c * 32 + lane;
-    const uint32_t m = t < a.T ? a.local_mask[t] : 0u;
-#pragma unroll
-    for (int le = 0; le < kELocal; ++le) {
-      const int n = __popc(__ballot_sync(0xFFFFFFFFu, (m >> le) & 1u));
-      if (lane == le) cnt += n;
-    }
-  }
+  for (int c = c0; c < c1; ++c) cnt += counted ? a.chunk_base[c * kELocal + lane] : chunk_counts(a, c, lane);
   s_wcount[warp][lane] = cnt;
   __syncthreads();
   if (warp == 0) {
@@ -165,14 +172,9 @@ __device__ void permute_block(const PermuteArgs& a) {
     if (fill_here) {
       base = fill_chunk(a, c, base, lane);
     } else {
-      a.chunk_base[c * kELocal + lane] = base;
-      const int t = c * 32 + lane;
-      const uint32_t m = t < a.T ? a.local_mask[t] : 0u;
-#pragma unroll
-      for (int le = 0; le < kELocal; ++le) {
-        const int n = __popc(__ballot_sync(0xFFFFFFFFu, (m >> le) & 1u));
-        if (lane == le) base += n;
-      }
+      const int n = counted ? a.chunk_base[c * kELocal + lane] : chunk_counts(a, c, lane);
+      a.chunk_base[c * kELocal + lane] = base;      // the count is replaced by the chunk's first row
+      base += n;
     }
   }
 }
@@ -262,10 +264,21 @@ __global__ void __launch_bounds__(256) route_block_kernel(RouteArgs a) {
   }
 }
 
-__global__ void __launch_bounds__(1024) permute_kernel(PermuteArgs a) {
+__global__ void __launch_bounds__(1024) permute_kernel(PermuteArgs a, bool counted) {
   griddep_launch_dependents();
   griddep_wait();
-  permute_block(a);
+  permute_block(a, counted);
+}
+
+// Large batches: the histogram of every 32-token chunk by one warp each, over many CTAs, so that the single
+// permutation CTA only scans 32 numbers per chunk instead of balloting through every token's mask.
+__global__ void __launch_bounds__(256) chunk_count_kernel(PermuteArgs a) {
+  griddep_launch_dependents();
+  griddep_wait();
+  const int lane = threadIdx.x & 31;
+  const int chunks = (a.T + 31) / 32;
+  for (int c = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); c < chunks; c += gridDim.x * (blockDim.x >> 5))
+    a.chunk_base[c * kELocal + lane] = chunk_counts(a, c, lane);
 }
 
 // Large batches: one warp per 32-token chunk fills the rows from the published chunk bases.
@@ -288,7 +301,7 @@ __global__ void __launch_bounds__(1024) route_permute_kernel(RouteArgs r, Permut
   route_tokens_strided(r, bias_smem, threadIdx.x >> 5, 32, threadIdx.x & 31);
   __threadfence_block();
   __syncthreads();
-  permute_block(p);
+  permute_block(p, false);
 }
 
 // Packed copy of the fp8 activation rows in permuted order: a_packed[r, :] = hidden[perm_token[r], :]
@@ -325,11 +338,11 @@ void launch_route_permute(const RouteArgs& r, const PermuteArgs& p, cudaStream_t
     launch_pdl(route_permute_kernel, dim3(1), dim3(1024), 0, stream, r, p);
   } else {
     launch_route_only(r, stream);
-    launch_pdl(permute_kernel, dim3(1), dim3(1024), 0, stream, p);
-    if (r.T > kPermuteFillInline) {
-      const int chunks = (r.T + 31) / 32;
-      launch_pdl(permute_fill_kernel, dim3((chunks + 7) / 8), dim3(256), 0, stream, p);
-    }
+    const bool big = r.T > kPermuteFillInline;
+    const int chunks = (r.T + 31) / 32;
+    if (big) launch_pdl(chunk_count_kernel, dim3((chunks + 7) / 8), dim3(256), 0, stream, p);
+    launch_pdl(permute_kernel, dim3(1), dim3(1024), 0, stream, p, big);
+    if (big) launch_pdl(permute_fill_kernel, dim3((chunks + 7) / 8), dim3(256), 0, stream, p);
   }
 }
 
