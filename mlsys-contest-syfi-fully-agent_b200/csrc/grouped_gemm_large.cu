@@ -58,15 +58,15 @@ static_assert(128 * kLRegsControl + kLEpiThreads * kLRegsEpi <= kLRegsAtLaunch *
 template <int GEMM>
 struct LCfg {
   static constexpr int KB = GEMM == 1 ? kKB1 : kKB2;             // K-blocks of the contraction
-  static constexpr int J = GEMM == 1 ? kKB2 : kMT2;              // weight-side units per token tile: 16 / 56
+  static constexpr int J = GEMM == 1 ? kKB2 : kMT2 / 2;          // weight-side units per token tile: 16 / 28
   static constexpr int NTERMS = GEMM == 1 ? 1 : kNTerms;         // e4m3 planes of the token operand
-  static constexpr int W_ROWS = GEMM == 1 ? 256 : 128;           // weight rows of an item = UMMA N = TMEM columns per K-block
+  static constexpr int W_ROWS = 256;                             // weight rows of an item = UMMA N = TMEM columns per K-block
   static constexpr int W_BYTES = W_ROWS * 128;                   // one K-block of the weight operand
   static constexpr int TOK_BYTES = 128 * 128;                    // one K-block of 128 token rows (one plane)
-  static constexpr int STAGE_BYTES = W_BYTES + NTERMS * TOK_BYTES;   // one K-block per pipeline stage: 48 KB / 64 KB
-  static constexpr int STAGES = GEMM == 1 ? 4 : 3;
+  static constexpr int STAGE_BYTES = W_BYTES + NTERMS * TOK_BYTES;   // one K-block per pipeline stage: 48 KB / 80 KB
+  static constexpr int STAGES = GEMM == 1 ? 4 : 2;
   static constexpr int BUF_COLS = W_ROWS;                        // TMEM columns of one stage's partial sums
-  static constexpr int NBUF = GEMM == 1 ? 2 : 3;                 // not deeper than the stage ring
+  static constexpr int NBUF = 2;                                 // not deeper than the stage ring
   static constexpr int TMEM_COLS = 512;
   static constexpr int AUX_BYTES = 4096;
   static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + AUX_BYTES + 1024;
@@ -194,7 +194,8 @@ grouped_gemm_large_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid
               tma_load_3d(dst + 128 * 128, &tm_w, 0, y + kI, kb, bar);
               tma_load_3d(dst + C::W_BYTES, &tm_b, 0, w.row0, kb, bar);                   // [128 rows][128 B]
             } else {
-              tma_load_3d(dst, &tm_w, 0, w.e * kH + w.j * 128, kb, bar);
+              tma_load_3d(dst, &tm_w, 0, w.e * kH + w.j * 256, kb, bar);                  // 256 weight rows as two boxes
+              tma_load_3d(dst + 128 * 128, &tm_w, 0, w.e * kH + w.j * 256 + 128, kb, bar);
               tma_load_4d(dst + C::W_BYTES, &tm_b, 0, w.row0, 0, kb, bar);                // [3 planes][128 rows][128 B]
             }
             if (++stage == C::STAGES) { stage = 0; ph ^= 1u; }
@@ -323,51 +324,57 @@ grouped_gemm_large_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid
           if (cg == 0) a.c_scale[static_cast<size_t>(row) * kKB2 + w.j] = __uint_as_float(static_cast<uint32_t>(ex + 127) << 23);
         }
       } else {
+        // this thread's 64 columns lie in ONE 128-row weight block: 2 j + (cg >> 1)
+        const int tile = 2 * w.j + (cg >> 1);
         const float* bsp = a.b_scale + static_cast<size_t>(lrow) * kKB2;
-        const float* wsp = a.w_scale + (static_cast<size_t>(w.e) * kMT2 + w.j) * kKB2;
-        float acc[32];
+        const float* wsp = a.w_scale + (static_cast<size_t>(w.e) * kMT2 + tile) * kKB2;
+        float acc[64];
 #pragma unroll
-        for (int x = 0; x < 32; ++x) acc[x] = 0.0f;
+        for (int x = 0; x < 64; ++x) acc[x] = 0.0f;
         float nb = __ldg(bsp), nw = __ldg(wsp);
 #pragma unroll 1
         for (int s = 0; s < kKB2; ++s) {
           if (!mbar_wait(done_base + stage * 8, ph, abort_flag)) { ok = false; break; }
           tc_fence_after_sync();
+          const uint32_t taddr = tmem_base + lane_addr + buf * C::BUF_COLS + cg * 64;
           float v[32];
-          tmem_ld32(tmem_base + lane_addr + buf * C::BUF_COLS + cg * 32, v);
+          tmem_ld32(taddr, v);
           const float f = nw * nb;
           if (s + 1 < kKB2) { nb = __ldg(bsp + s + 1); nw = __ldg(wsp + s + 1); }
+          tmem_wait_ld();
+          fma32(acc, v, f);
+          tmem_ld32(taddr + 32, v);
           tmem_wait_ld();
           tc_fence_before_sync();
           __syncwarp();
           if (lane == 0) mbar_arrive(tempty_base + buf * 8);
-          fma32(acc, v, f);
+          fma32(acc + 32, v, f);
           if (++stage == C::STAGES) { stage = 0; ph ^= 1u; }
           if (++buf == C::NBUF) { buf = 0; bph ^= 1u; }
         }
         if (!ok) break;
         if (trow < w.valid) {
-          const int col0 = w.j * 128 + cg * 32;
+          const int col0 = w.j * 256 + cg * 64;
           if constexpr (!COMBINE) {
             float* out = a.out + static_cast<size_t>(row) * kH + col0;
 #pragma unroll
-            for (int x = 0; x < 4; ++x) st_global_v8(out + 8 * x, acc + 8 * x);   // whole 32-byte sectors
+            for (int x = 0; x < 8; ++x) st_global_v8(out + 8 * x, acc + 8 * x);   // whole 32-byte sectors
           } else {
             const int t = __ldcg(a.perm_token + row);
             const float pw = __ldcg(a.perm_weight + row);
             float* dst = a.acc32 + static_cast<size_t>(t) * kH + col0;
 #pragma unroll
-            for (int x = 0; x < 8; ++x)
+            for (int x = 0; x < 16; ++x)
               red_add_v4(dst + 4 * x, __fmul_rn(acc[4 * x], pw), __fmul_rn(acc[4 * x + 1], pw), __fmul_rn(acc[4 * x + 2], pw),
                          __fmul_rn(acc[4 * x + 3], pw));
             __threadfence();      // the reductions above are performed before the arrival below is
-            const int target = 4 * __popc(__ldcg(a.local_mask + t));   // four column groups per (row, column tile)
-            const int old = atomicAdd(a.tile_cnt + static_cast<size_t>(t) * kMT2 + w.j, 1);
+            const int target = 2 * __popc(__ldcg(a.local_mask + t));   // two threads per (row, 128-column tile)
+            const int old = atomicAdd(a.tile_cnt + static_cast<size_t>(t) * kMT2 + tile, 1);
             if (old == target - 1) {
               // last contributor of (token, column tile): all 128 sums are complete
               __threadfence();
-              const float4* src = reinterpret_cast<const float4*>(a.acc32 + static_cast<size_t>(t) * kH + w.j * 128);
-              uint16_t* orow = (a.out_rows ? a.out_rows[t] : a.out_bf16 + static_cast<size_t>(t) * kH) + w.j * 128;
+              const float4* src = reinterpret_cast<const float4*>(a.acc32 + static_cast<size_t>(t) * kH + tile * 128);
+              uint16_t* orow = (a.out_rows ? a.out_rows[t] : a.out_bf16 + static_cast<size_t>(t) * kH) + tile * 128;
 #pragma unroll
               for (int h = 0; h < 2; ++h) {
                 float4 u[16];

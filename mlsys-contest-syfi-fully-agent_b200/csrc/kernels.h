@@ -63,7 +63,7 @@ struct PermuteArgs {
   int* tok_rows;                // [T, 8] rows of a token in ascending local expert order
   int* chunk_base;              // [ceil(T / 32), 32] first row of every (32-token chunk, expert); large T only
   int large;                    // 1: GEMM1 with the SwiGLU epilogue (no split-K, items are (token tile, 128-column block of C));
-                                // 2: also GEMM2 with the fused combine (no split-K either)
+                                // 2: also the large-batch GEMM2 (no split-K either, items are (token tile, 256 weight rows))
 };
 
 struct GatherArgs {

@@ -335,7 +335,7 @@ static int run_impl(const float* routing_logits, const uint16_t* routing_bias, c
   RouteArgs ra{routing_logits, routing_bias, T, local_expert_offset, routed_scaling_factor, topk_idx, topk_w,
                local_mask};
   PermuteArgs pa{T, local_expert_offset, n_tile, n_tile2, ctas, static_cast<int>(kps1), static_cast<int>(kps2), L.rows_cap, L.slab_rows, local_mask, topk_idx, topk_w,
-                 sched, perm_token, perm_weight, tok_rows, chunk_base, fast_combine ? 2 : large ? 1 : 0};
+                 sched, perm_token, perm_weight, tok_rows, chunk_base, large ? 2 : 0};
   stage_mark(0, stream);
   launch_route_permute(ra, pa, stream);
   MOE_CUDA(cudaGetLastError());
@@ -373,9 +373,7 @@ static int run_impl(const float* routing_logits, const uint16_t* routing_bias, c
     g_launches += 1;
     stage_mark(3, stream);
     stage_mark(4, stream);      // no SwiGLU kernel on this path
-    // GEMM2: the 16-warp kernel only for the fused combine; for fp32 rows the eight-warp kernel measures faster
-    if ((rc = fast_combine ? launch_grouped_gemm_large(2, true, tm_w2, tm_c, g2a, ctas, stream)
-                           : launch_grouped_gemm(2, n_tile2, tm_w2, tm_c, g2a, ctas, stream))) {
+    if ((rc = launch_grouped_gemm_large(2, fast_combine, tm_w2, tm_c, g2a, ctas, stream))) {
       g_last_cuda_error = rc;
       return MOE_B200_ECUDA;
     }

@@ -160,7 +160,7 @@ __device__ void permute_block(const PermuteArgs& a, bool counted) {
       sc->split1 = s1;
       sc->split2 = s2;
       sc->items1 = a.large ? tiles_total * kKB2 : tiles_total * kMT1 * s1;   // large: one item per 128-column block of C
-      sc->items2 = tiles_total2 * kMT2 * s2;
+      sc->items2 = a.large > 1 ? tiles_total2 * (kMT2 / 2) : tiles_total2 * kMT2 * s2;   // large: 256-row weight units
     }
   }
   __syncthreads();
