@@ -60,9 +60,10 @@ EP_REFERENCE_SAMPLE = 4       # tokens of it that the CPU arm pushes through all
 
 # dram__bytes_read.sum + dram__bytes_write.sum of one launch of the dominant kernel, from ncu captures of the
 # same command (None where no capture of that workload exists).
-NCU_TRAFFIC_BYTES = {"decode_t1": 88_237_568 + 2_996_224,
-                     "skew_t64": 473_900_000 + 12_800_000,
-                     "prefill_t4096": 807_600_000 + 67_100_000}
+NCU_TRAFFIC_BYTES = {"decode_t1": 88_247_000 + 3_136_000,        # decode_kernel
+                     "skew_t64": 473_900_000 + 12_800_000,       # grouped_gemm_kernel<1,64>
+                     "mid_t512": 593_900_000 + 7_900_000,        # grouped_gemm_kernel<1,64>
+                     "prefill_t4096": 829_100_000 + 35_300_000}  # grouped_gemm_large_kernel<1>
 
 W13_BYTES = 4096 * 7168 + 32 * 56 * 4          # one expert's GEMM1 weights + scales
 W2_BYTES = 7168 * 2048 + 56 * 16 * 4
