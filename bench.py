@@ -904,6 +904,65 @@ def reference_cuda_rows():
     return {"unavailable": f"child exited {r.returncode}: {(r.stderr or r.stdout)[-300:]}"}
 
 
+# sequence lengths of the stand-in trace set (`--replay synthetic`): the five single-GPU configurations plus
+# ragged sizes either side of the kernel-path boundaries (16 / 1024 tokens)
+REPLAY_SEQ_LENS = (1, 8, 16, 17, 53, 64, 130, 512, 1024, 1025, 4096)
+
+
+def bench_replay(args):
+    """Replays a flashinfer-trace workload set (or a stand-in written on the spot) through the operator with the
+    harness's settings, the oracle as the checker, and prints the per-workload table as one JSON line.  When the
+    reference's CUDA solution has been built, it is timed on the same tensors as each workload's reference latency."""
+    import tempfile
+    pkg = load_package()
+    oracle = load_oracle()
+    rp = pkg.replay
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    root, data = args.replay, "trace set"
+    tmp = None
+    if root == "synthetic":
+        tmp = tempfile.TemporaryDirectory()
+        root = tmp.name
+        rp.write_synthetic_trace(root, REPLAY_SEQ_LENS, seed=0)
+        data = "synthetic stand-in set in the flashinfer-trace layout (routing logits and bias stored, the rest seeded)"
+    ref_ms = rp.load_ref_cache(args.ref_cache) if args.ref_cache else {}
+    weights = pkg.gen.make_shard_weights(0, dev)
+    if not ref_ms and os.path.exists(REF_CUDA_LIB):
+        ref_ms = replay_reference_cuda(rp, root, weights, dev)
+    res = rp.replay(root, device=dev, checker=oracle.harness_check, ref_latency_ms=ref_ms, weights=weights,
+                    limit=args.replay_limit)
+    res["replay"] = {"root": args.replay, "data": data, "definition": rp.DEFINITION,
+                     "settings": dict(rp.BENCH_DEFAULTS),
+                     "ref_latency": ("cache file" if args.ref_cache else
+                                     "the reference's CUDA solution timed here on the same tensors" if ref_ms else None)}
+    print(json.dumps(res))
+    if tmp is not None:
+        tmp.cleanup()
+    assert res["error"] is None and res["correct"], [(p["axes"], p["status"]) for p in res["per_workload"]]
+
+
+def replay_reference_cuda(rp, root, weights, dev):
+    """{uuid: ms} of the reference's own CUDA solution on every workload of the set (same protocol as ours)."""
+    import tvm_ffi
+    run = tvm_ffi.load_module(REF_CUDA_LIB).run
+    out = {}
+    files = {}
+    for wl in rp.read_workloads(root):
+        if wl.seq_len == 0:
+            continue
+        try:
+            inp = rp.materialise(wl, root, dev, weights=weights, _files=files)
+        except rp.TraceError:
+            continue
+        o = torch.empty(wl.seq_len, H, dtype=torch.bfloat16, device=dev)
+        a = [inp[n] for n in rp.INPUT_ORDER] + [o]
+        trials = rp.time_workload(lambda: run(*a), dev, rp.BENCH_DEFAULTS["warmup_runs"], rp.BENCH_DEFAULTS["iterations"],
+                                  rp.BENCH_DEFAULTS["num_trials"])
+        out[wl.uuid] = sum(trials) / len(trials)
+    return out
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -915,8 +974,15 @@ def main():
     ap.add_argument("--profile-only", action="store_true",
                     help="run W + K steps of the workload and exit (no checks, no CPU legs): the command profiler "
                          "captures are taken from")
+    ap.add_argument("--replay", default=None, metavar="ROOT",
+                    help="replay a flashinfer-trace workload set rooted at ROOT ('synthetic': a stand-in set written to "
+                         "a temporary directory) and print the per-workload table")
+    ap.add_argument("--ref-cache", default=None, help="reference latencies for --replay ({uuid: {ref_latency_ms}})")
+    ap.add_argument("--replay-limit", type=int, default=0, help="cap the number of replayed workloads (0 = all)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
+    if args.replay:
+        return bench_replay(args)
     if args.profile_only:
         return profile_only(args)
     if args.impl == "reference":

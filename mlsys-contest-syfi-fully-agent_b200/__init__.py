@@ -11,6 +11,7 @@ Sub-modules:
   ep      expert-parallel 256-expert layer over torch.distributed
   build   nvcc build of csrc/ for sm_100a
   packaging  config.toml + solution.json in the reference's schema
+  replay  a flashinfer-trace workload set run through ``op.run`` (per-workload status, latency, speed-up)
 """
 from . import gen  # noqa: F401
 
@@ -18,7 +19,7 @@ from . import gen  # noqa: F401
 def __getattr__(name):
     # torch-free / CUDA-free modules are imported eagerly above; the ones that
     # need the compiled library are resolved on first use.
-    if name in ("loader", "op", "ep", "build", "packaging"):
+    if name in ("loader", "op", "ep", "build", "packaging", "replay"):
         import importlib
         return importlib.import_module(f"{__name__}.{name}")
     raise AttributeError(name)

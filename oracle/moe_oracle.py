@@ -247,3 +247,40 @@ PARITY_KEYS = ("max_abs_over_rms", "cosine", "n", "n_diff", "n_one_step", "n_mul
 def parity_report(m: dict) -> dict:
     """The subset of ``output_metrics`` that the benchmark prints with every measured row."""
     return {k: m[k] for k in PARITY_KEYS if k in m}
+
+
+def harness_check(inputs: dict, out_bf16: torch.Tensor, required_matched_ratio: float = 0.999,
+                  cpu_max_tokens: int = 64) -> dict:
+    """Verdict on one workload of a replayed trace set, with the quantities the reference's harness
+    reports per workload (full-agent-pipeline/run_pipeline.py:436-438: max absolute and relative error) at
+    its tolerances rtol = atol = 1e-2 (run_pipeline.py:300-307).  ``inputs`` maps the operator's ten input
+    names to values; the oracle runs on the host up to ``cpu_max_tokens`` tokens, beyond that on the device
+    of the inputs in fp32 with TF32 off.  Passed: the share of elements within atol + rtol * |reference| is
+    at least ``required_matched_ratio`` and the cosine at least 0.9999."""
+    T = int(inputs["routing_logits"].shape[0])
+    if T == 0:
+        return {"passed": out_bf16.numel() == 0, "max_abs_err": 0.0, "max_rel_err": 0.0, "match_ratio": 1.0,
+                "cosine": 1.0, "oracle_on": "none"}
+    names = ("routing_logits", "routing_bias", "hidden_states", "hidden_states_scale")
+    wnames = ("gemm1_weights", "gemm1_weights_scale", "gemm2_weights", "gemm2_weights_scale")
+    off, rsf = int(inputs["local_expert_offset"]), float(inputs["routed_scaling_factor"])
+    if T <= cpu_max_tokens:
+        cache = {}
+
+        def ew(le):
+            if le not in cache:
+                cache[le] = tuple(inputs[n][le].cpu() for n in wnames)
+            return cache[le]
+        ref = run(*[inputs[n].cpu() for n in names], ew, off, rsf)
+        where = "cpu"
+    else:
+        torch.backends.cuda.matmul.allow_tf32 = False
+        ref = run_full(*[inputs[n] for n in names], *[inputs[n] for n in wnames], off, rsf)
+        where = "gpu_fp32"
+    m = output_metrics(out_bf16, ref.output, ref.output_f32)
+    a = out_bf16.to(torch.float64)
+    b = ref.output.to(out_bf16.device).to(torch.float64)
+    rel = float(((a - b).abs() / (b.abs() + 1e-8)).max())
+    return {"passed": m["match_ratio"] >= required_matched_ratio and m["cosine"] >= 0.9999,
+            "max_abs_err": m["max_abs"], "max_rel_err": rel, "match_ratio": m["match_ratio"], "cosine": m["cosine"],
+            "max_abs_over_rms": m["max_abs_over_rms"], "oracle_on": where}
