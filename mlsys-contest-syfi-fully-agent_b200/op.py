@@ -32,7 +32,9 @@ class Workspace:
         self.nbytes = 0
 
     def reserve(self, T: int):
-        need = loader.workspace_bytes(T)
+        need = _ws_bytes.get(T)
+        if need is None:
+            need = _ws_bytes[T] = loader.workspace_bytes(T)
         if self._buf is None or need > self.nbytes:
             self._buf = torch.empty(need + 1024, dtype=torch.uint8, device=self.device)
             self._base = (-self._buf.data_ptr()) % 1024
@@ -48,6 +50,7 @@ class Workspace:
 
 
 _default_ws: Dict[int, Workspace] = {}
+_ws_bytes: Dict[int, int] = {}       # workspace size per token count (a library call otherwise)
 
 
 def _default_workspace(device: torch.device) -> Workspace:
@@ -62,20 +65,49 @@ def _check(cond: bool, msg: str):
         raise ValueError(msg)
 
 
-_validated = {}     # signature of the last argument set that passed _validate, per entry point
+_validated: Dict[tuple, bool] = {}     # signatures of argument sets that passed _validate
+_VALIDATED_MAX = 64
+
+
+def _stream_of(dev: torch.device) -> int:
+    """Handle of torch's current stream on ``dev``."""
+    try:
+        return torch._C._cuda_getCurrentRawStream(dev.index if dev.index is not None else torch.cuda.current_device())
+    except AttributeError:      # a torch build without the raw getter
+        return torch.cuda.current_stream(dev).cuda_stream
+
+
+class _on_device:
+    """``torch.cuda.device(dev)`` only when ``dev`` is not already current (the context manager costs
+    more host time than the launch it wraps)."""
+
+    def __init__(self, dev: torch.device):
+        self.ctx = None
+        if dev.index is not None and dev.index != torch.cuda.current_device():
+            self.ctx = torch.cuda.device(dev)
+
+    def __enter__(self):
+        if self.ctx is not None:
+            self.ctx.__enter__()
+
+    def __exit__(self, *exc):
+        if self.ctx is not None:
+            self.ctx.__exit__(*exc)
 
 
 def _validate(routing_logits, routing_bias, hidden_states, hidden_states_scale, gemm1_weights, gemm1_weights_scale,
               gemm2_weights, gemm2_weights_scale, output, device_inputs: bool):
+    """Checks the nine tensors the way the definition asserts them; returns (T, their addresses)."""
     T = routing_logits.shape[0]
-    # A serving loop calls with the same buffers again and again: an argument set whose addresses, dtypes and
-    # shapes equal the last validated one is not inspected a second time (the checks cost more host time
-    # than a decode step's launch).
+    # A serving loop calls with the same buffers again and again (or rotates over a few sets): an argument set
+    # whose addresses, dtypes and shapes equal a validated one is not inspected a second time (the checks cost
+    # more host time than a decode step's launch).
     args = (routing_logits, routing_bias, hidden_states, hidden_states_scale, gemm1_weights, gemm1_weights_scale,
             gemm2_weights, gemm2_weights_scale, output)
-    sig = tuple((t.data_ptr(), t.dtype, t.shape) for t in args)
-    if _validated.get(device_inputs) == sig:
-        return T
+    ptrs = tuple([t.data_ptr() for t in args])
+    sig = (device_inputs, ptrs, tuple([(t.dtype, t.shape) for t in args]))
+    if sig in _validated:
+        return T, ptrs
     _check(routing_logits.dtype == torch.float32 and tuple(routing_logits.shape) == (T, E_GLOBAL),
            "routing_logits must be float32 [T, 256]")
     _check(routing_bias.dtype == torch.bfloat16 and routing_bias.numel() == E_GLOBAL, "routing_bias must be bfloat16 [256]")
@@ -103,8 +135,10 @@ def _validate(routing_logits, routing_bias, hidden_states, hidden_states_scale, 
         _check(t.is_contiguous(), f"{name} must be contiguous")
         on_device = name.startswith("gemm") or device_inputs
         _check(t.is_cuda == on_device, f"{name} must live on the {'GPU' if on_device else 'host'}")
-    _validated[device_inputs] = sig
-    return T
+    if len(_validated) >= _VALIDATED_MAX:
+        _validated.clear()
+    _validated[sig] = True
+    return T, ptrs
 
 
 def run(routing_logits: torch.Tensor, routing_bias: torch.Tensor, hidden_states: torch.Tensor,
@@ -116,20 +150,17 @@ def run(routing_logits: torch.Tensor, routing_bias: torch.Tensor, hidden_states:
     [T, 7168]) is fully overwritten and returned; it is allocated when omitted."""
     if output is None:
         output = torch.empty((routing_logits.shape[0], H), dtype=torch.bfloat16, device=hidden_states.device)
-    T = _validate(routing_logits, routing_bias, hidden_states, hidden_states_scale, gemm1_weights,
-                  gemm1_weights_scale, gemm2_weights, gemm2_weights_scale, output, device_inputs=True)
+    T, ptrs = _validate(routing_logits, routing_bias, hidden_states, hidden_states_scale, gemm1_weights,
+                        gemm1_weights_scale, gemm2_weights, gemm2_weights_scale, output, device_inputs=True)
     if T == 0:
         return output
     dev = hidden_states.device
     ws = (workspace or _default_workspace(dev)).reserve(T)
-    with torch.cuda.device(dev):
-        stream = torch.cuda.current_stream(dev).cuda_stream
-        rc = loader.lib.moe_fp8_block_scale_run(
-            routing_logits.data_ptr(), routing_bias.data_ptr(), hidden_states.data_ptr(),
-            hidden_states_scale.data_ptr(), gemm1_weights.data_ptr(), gemm1_weights_scale.data_ptr(),
-            gemm2_weights.data_ptr(), gemm2_weights_scale.data_ptr(), int(T), int(local_expert_offset),
-            float(routed_scaling_factor), output.data_ptr(), ws.ptr, ws.nbytes, stream)
-    loader.check(rc)
+    with _on_device(dev):
+        rc = loader.lib.moe_fp8_block_scale_run(*ptrs[:8], T, int(local_expert_offset), float(routed_scaling_factor),
+                                                ptrs[8], ws.ptr, ws.nbytes, _stream_of(dev))
+    if rc:
+        loader.check(rc)
     return output
 
 
@@ -162,20 +193,18 @@ def run_host(routing_logits, routing_bias, hidden_states, hidden_states_scale, g
              output: torch.Tensor, workspace: Optional[Workspace] = None) -> torch.Tensor:
     """Same operator for token-side tensors in (pinned) host memory: copies them
     in, runs, copies ``output`` (a host tensor) back and waits."""
-    T = _validate(routing_logits, routing_bias, hidden_states, hidden_states_scale, gemm1_weights,
-                  gemm1_weights_scale, gemm2_weights, gemm2_weights_scale, output, device_inputs=False)
+    T, ptrs = _validate(routing_logits, routing_bias, hidden_states, hidden_states_scale, gemm1_weights,
+                        gemm1_weights_scale, gemm2_weights, gemm2_weights_scale, output, device_inputs=False)
     if T == 0:
         return output
     dev = gemm1_weights.device
     ws = (workspace or _default_workspace(dev)).reserve(T)
-    with torch.cuda.device(dev):
-        stream = torch.cuda.current_stream(dev).cuda_stream
-        rc = loader.lib.moe_fp8_block_scale_run_host(
-            routing_logits.data_ptr(), routing_bias.data_ptr(), hidden_states.data_ptr(),
-            hidden_states_scale.data_ptr(), gemm1_weights.data_ptr(), gemm1_weights_scale.data_ptr(),
-            gemm2_weights.data_ptr(), gemm2_weights_scale.data_ptr(), int(T), int(local_expert_offset),
-            float(routed_scaling_factor), output.data_ptr(), ws.ptr, ws.nbytes, stream)
-    loader.check(rc)
+    with _on_device(dev):
+        rc = loader.lib.moe_fp8_block_scale_run_host(*ptrs[:8], T, int(local_expert_offset),
+                                                     float(routed_scaling_factor), ptrs[8], ws.ptr, ws.nbytes,
+                                                     _stream_of(dev))
+    if rc:
+        loader.check(rc)
     return output
 
 

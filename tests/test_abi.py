@@ -82,3 +82,30 @@ def test_operator_argument_validation(pkg, loader):
             op._validate(*[kw[k] for k in ("routing_logits", "routing_bias", "hidden_states", "hidden_states_scale",
                                           "gemm1_weights", "gemm1_weights_scale", "gemm2_weights",
                                           "gemm2_weights_scale", "output")], device_inputs=False)
+
+
+def test_refused_argument_sets_are_not_remembered(pkg, loader):
+    """The wrapper skips the checks for argument sets it has validated before; a set it refused must
+    not enter that memory."""
+    op = pkg.op
+    T = 3
+    w13 = torch.zeros(1, dtype=torch.float8_e4m3fn).expand(32, 4096, 7168)
+    w2 = torch.zeros(1, dtype=torch.float8_e4m3fn).expand(32, 7168, 2048)
+
+    def make():
+        return (torch.zeros(T, 256), torch.zeros(256, dtype=torch.bfloat16), torch.zeros(T, 7168).to(torch.float8_e4m3fn),
+                torch.zeros(56, T), w13, torch.zeros(32, 32, 56), w2, torch.zeros(32, 56, 16),
+                torch.zeros(T, 7168, dtype=torch.bfloat16))
+    op._validated.clear()
+    sets = [make() for _ in range(3)]
+    for a in sets:
+        # (expanded weights are not contiguous: this set is refused, and a refused set is not remembered)
+        with pytest.raises(ValueError):
+            op._validate(*a, device_inputs=False)
+    assert len(op._validated) == 0
+    sets = [a[:4] + (torch.zeros(32, 1, 1).to(torch.float8_e4m3fn),) + a[5:6] + (torch.zeros(32, 1, 1).to(torch.float8_e4m3fn),) + a[7:]
+            for a in sets]
+    for a in sets:
+        with pytest.raises(ValueError):      # wrong weight shape
+            op._validate(*a, device_inputs=False)
+    assert len(op._validated) == 0
