@@ -652,8 +652,9 @@ def bench_ep(args):
     torch.cuda.empty_cache()
 
     # ---- the same layer call from host buffers: this rank's token tensors come from pinned host memory and its
-    # output rows go back to pinned host memory inside the timed region.  The copies run on a second stream with
-    # two sets of device buffers, so step k + 1's inputs and step k - 1's output travel while step k computes.
+    # output rows go back to pinned host memory inside the timed region.  The copies run on two more streams (one per
+    # direction) with two sets of device buffers, so step k + 1's inputs and step k - 1's output travel while step k
+    # computes.
     layer = ep.ExpertParallelMoE(weights, rank, world, transport=transports[0])
     pin = lambda t: t.cpu().pin_memory()
     h_in = [pin(logits), pin(bias), pin(hidden.view(torch.uint8)), pin(hscale)]
@@ -661,7 +662,8 @@ def bench_ep(args):
              torch.empty_like(hscale)] for _ in range(2)]
     d_out = [torch.empty((T, H), dtype=torch.bfloat16, device=dev) for _ in range(2)]
     h_out = torch.empty((T, H), dtype=torch.bfloat16).pin_memory()
-    copy_stream = torch.cuda.Stream(device=dev)
+    copy_stream = torch.cuda.Stream(device=dev)      # host -> device
+    back_stream = torch.cuda.Stream(device=dev)      # device -> host: its own stream, so both directions of the link run at once
     main = torch.cuda.current_stream(dev)
     in_ready = [torch.cuda.Event() for _ in range(2)]
     in_free = [torch.cuda.Event() for _ in range(2)]
@@ -690,11 +692,12 @@ def bench_ep(args):
             d_out[b].copy_(o)
             in_free[b].record(main)
             out_ready[b].record(main)
-            with torch.cuda.stream(copy_stream):
-                copy_stream.wait_event(out_ready[b])
+            with torch.cuda.stream(back_stream):
+                back_stream.wait_event(out_ready[b])
                 h_out.copy_(d_out[b], non_blocking=True)
-                out_free[b].record(copy_stream)
+                out_free[b].record(back_stream)
         main.wait_stream(copy_stream)
+        main.wait_stream(back_stream)
 
     host_loop(3)
     sync()
@@ -743,7 +746,7 @@ def bench_ep(args):
             "e2e": {"value": EP_T / (ms_host * 1e-3), "unit": UNIT, "ms_per_step": ms_host,
                     "h2d_bytes_per_step": h2d * world, "d2h_bytes_per_step": d2h * world,
                     "note": "every rank copies its token tensors from pinned host memory and its output rows back; "
-                            "copies on a second stream, double buffered"},
+                            "copies on two more streams (one per direction), double buffered"},
             "roofline": dom,
             "per_gpu": roofline("whole layer call on the most loaded rank", per * 32 * (W13_BYTES + W2_BYTES),
                                 EP_T * 8 * rows_max / total_rows * (FLOPS1 + FLOPS2), ms_step * 1e3, None, P,

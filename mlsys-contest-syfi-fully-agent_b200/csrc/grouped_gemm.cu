@@ -63,6 +63,13 @@ struct Cfg {
   // because the instruction queue behind the issuing thread is only an instruction or two deep.
   static constexpr int ISSUERS = N_TILE >= 32 ? 2 : 1;
   static constexpr bool TOK_ON_M = N_TILE == 128 && GEMM == 1;   // (GEMM2 measures the same either way)
+  // Ragged token tiles (swapped orientation only): an item brings and multiplies the rows it has, rounded up to
+  // RSTEP.  An SM takes in about 45 bytes per clock from L2 and HBM delivers a 16 KB weight tile every ~700
+  // clocks per SM, so a K-block may cost 31 KB of operands before the weight stream stalls; GEMM2's three
+  // planes of a full 64-token tile alone are 24 KB.
+  static constexpr int RSTEP = N_TILE >= 64 ? N_TILE / 4 : 16;
+  static constexpr int RMAPS = N_TILE / RSTEP;
+  static_assert(RMAPS >= 1 && RMAPS <= 4 && RSTEP % 16 == 0, "token maps per kernel / UMMA N granularity");
   static constexpr int A_BYTES = 128 * 128;
   static constexpr int B_BYTES = N_TILE * 128;
   static constexpr int KB_BYTES = A_BYTES + NTERMS * B_BYTES;           // operands of one K-block
@@ -101,6 +108,7 @@ struct Cfg {
 
 struct Item {
   int e, m, s, row0, valid, kb0, kb1;
+  int nv;      // token rows the item brings and multiplies: `valid` rounded up to the row step
 };
 
 template <int GEMM, int N_TILE>
@@ -124,6 +132,7 @@ __device__ __forceinline__ Item decode_item(int i, int split, const Aux* aux) {
   const int cnt = aux->offs[e + 1] - aux->offs[e];
   it.row0 = aux->offs[e] + n * N_TILE;
   it.valid = min(N_TILE, cnt - n * N_TILE);
+  it.nv = C::TOK_ON_M ? N_TILE : min(N_TILE, (it.valid + C::RSTEP - 1) / C::RSTEP * C::RSTEP);
   // split boundaries in units of one pipeline stage, so that no stage straddles two items
   constexpr int kUnits = C::KB / C::KPS;
   it.kb0 = ((it.s * kUnits) / split) * C::KPS;
@@ -133,7 +142,7 @@ __device__ __forceinline__ Item decode_item(int i, int split, const Aux* aux) {
 
 template <int GEMM, int N_TILE>
 __global__ void __launch_bounds__(kThreads, 1)
-grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_b, GemmArgs a) {
+grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ TokenMaps tm_b, GemmArgs a) {
   using C = Cfg<GEMM, N_TILE>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -155,7 +164,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
     mbar_init(smem_u32(&aux->esync), kEpiWarps * 32);
     fence_mbar_init();
     tma_prefetch_desc(&tm_w);
-    tma_prefetch_desc(&tm_b);
+    for (int i = 0; i < C::RMAPS; ++i) tma_prefetch_desc(&tm_b.m[i]);
   }
   if (warp == 1) {
     tmem_alloc(smem_u32(&aux->tmem_base), C::TMEM_COLS);
@@ -192,12 +201,13 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
         for (int kb = w.kb0; kb < w.kb1; kb += C::KPS) {
           if (!mbar_wait(done_base + stage * 8, ph ^ 1u, abort_flag)) { ok = false; break; }
           const uint32_t bar = full_base + stage * 8;
-          mbar_arrive_expect_tx(bar, C::STAGE_BYTES);
+          mbar_arrive_expect_tx(bar, C::KPS * (C::A_BYTES + C::NTERMS * w.nv * 128));
           const uint32_t dst = smem_base + stage * C::STAGE_BYTES;
-          // weights: [KPS][128 rows][128 B]; tokens: [KPS][NTERMS planes][N_TILE rows][128 B]
+          // weights: [KPS][128 rows][128 B]; tokens: [KPS][NTERMS planes][nv rows][128 B]
           tma_load_3d(dst, &tm_w, 0, wy, kb, bar);
-          if (GEMM == 1) tma_load_3d(dst + C::KPS * C::A_BYTES, &tm_b, 0, by, kb, bar);
-          else tma_load_4d(dst + C::KPS * C::A_BYTES, &tm_b, 0, by, 0, kb, bar);
+          const CUtensorMap* mb = &tm_b.m[w.nv / C::RSTEP - 1];
+          if (GEMM == 1) tma_load_3d(dst + C::KPS * C::A_BYTES, mb, 0, by, kb, bar);
+          else tma_load_4d(dst + C::KPS * C::A_BYTES, mb, 0, by, 0, kb, bar);
           if (++stage == C::STAGES) { stage = 0; ph ^= 1u; }
         }
       }
@@ -209,7 +219,6 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
     // dependent-issue latency), so ring positions are kept incrementally and the descriptors are
     // formed with one add from constants.
     if (lane == 0) {
-      constexpr uint32_t idesc = umma_idesc_e4m3(128, C::N_MMA);
       const uint64_t desc_const = umma_desc_k_sw128(0);          // everything but the start address
       const uint32_t smem_base = smem_u32(smem);
       const uint32_t full_base = smem_u32(&aux->full[0]), done_base = smem_u32(&aux->done[0]);
@@ -219,6 +228,8 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
       [[maybe_unused]] int nst = 0;
       for (int i = blockIdx.x; ok && i < items; i += gridDim.x) {
         const Item w = decode_item<GEMM, N_TILE>(i, split, aux);
+        const uint32_t idesc = umma_idesc_e4m3(128, C::STACK ? C::NTERMS * w.nv : w.nv);
+        const uint32_t plane_bytes = static_cast<uint32_t>(w.nv) * 128;
         for (int kb = w.kb0; kb < w.kb1; kb += C::KPS, ++nst) {        // items span whole stages
           if (C::ISSUERS == 2 && (nst & 1) != warp - 1) {               // the other issuer's stage
             if (++stage == C::STAGES) { stage = 0; ph ^= 1u; }
@@ -232,11 +243,11 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
 #pragma unroll
           for (int u = 0; u < C::KPS; ++u) {
             const uint64_t adesc = desc_const | ((sbase + u * C::A_BYTES) >> 4);
-            const uint32_t sb = sbase + C::KPS * C::A_BYTES + u * (C::NTERMS * C::B_BYTES);
+            const uint32_t sb = sbase + C::KPS * C::A_BYTES + u * (C::NTERMS * plane_bytes);
             const uint32_t d = tmem_base + buf * (C::G * C::KB_COLS) + u * C::KB_COLS;
 #pragma unroll
             for (int t = 0; t < C::MMA_PER_K4; ++t) {
-              const uint64_t bdesc = desc_const | ((sb + t * C::B_BYTES) >> 4);
+              const uint64_t bdesc = desc_const | ((sb + t * plane_bytes) >> 4);
 #pragma unroll
               for (int k4 = 0; k4 < 4; ++k4) {  // +32 bytes of K inside the 128-byte swizzle atom = +2 encoded units
                 if constexpr (C::TOK_ON_M) umma_f8(d, bdesc + 2 * k4, adesc + 2 * k4, idesc, (t | k4) != 0 ? 1u : 0u);
@@ -361,18 +372,23 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
 #pragma unroll
         for (int g = 0; g < C::G; ++g) {
           // one K-block's partial at a time, in chunks of at most 64 columns (register budget);
-          // the buffer is released after the last read
+          // the buffer is released after the last read.  The stacked planes are w.nv columns apart.  A chunk
+          // that starts past the item's rows is not read (its columns are never stored; whole warps skip it).
 #pragma unroll
           for (int c0 = 0; c0 < C::CPW; c0 += C::CH) {
             float v[C::PLANES][C::CH];
+            const bool live = h * C::CPW + c0 < w.nv;
+            if (live) {
 #pragma unroll
-            for (int p = 0; p < C::PLANES; ++p) tmem_ld_cols<C::CH>(taddr + g * C::KB_COLS + p * N_TILE + c0, v[p]);
-            tmem_wait_ld();
+              for (int p = 0; p < C::PLANES; ++p) tmem_ld_cols<C::CH>(taddr + g * C::KB_COLS + p * w.nv + c0, v[p]);
+              tmem_wait_ld();
+            }
             if (g == C::G - 1 && c0 + C::CH >= C::CPW) {
               tc_fence_before_sync();
               __syncwarp();
               if (lane == 0) mbar_arrive(tempty_base + buf * 8);
             }
+            if (!live) continue;
             const float4* scv = reinterpret_cast<const float4*>(sc + (kbl + g) * N_TILE + h * C::CPW + c0);
 #pragma unroll
             for (int u = 0; u < C::CH / 4; ++u) {
@@ -431,7 +447,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
 }
 
 template <int GEMM, int N_TILE>
-int launch_one(const CUtensorMap& tm_w, const CUtensorMap& tm_b, const GemmArgs& a, int ctas, cudaStream_t stream) {
+int launch_one(const CUtensorMap& tm_w, const TokenMaps& tm_b, const GemmArgs& a, int ctas, cudaStream_t stream) {
   using C = Cfg<GEMM, N_TILE>;
   return static_cast<int>(launch_pdl(grouped_gemm_kernel<GEMM, N_TILE>, dim3(ctas), dim3(kThreads), C::SMEM_BYTES,
                                      stream, tm_w, tm_b, a));
@@ -469,7 +485,9 @@ int grouped_gemm_init() {
   return 0;
 }
 
-int launch_grouped_gemm(int gemm_id, int n_tile, const CUtensorMap& tm_w, const CUtensorMap& tm_b, const GemmArgs& a,
+int grouped_gemm_row_step(int n_tile) { return n_tile >= 64 ? n_tile / 4 : 16; }
+
+int launch_grouped_gemm(int gemm_id, int n_tile, const CUtensorMap& tm_w, const TokenMaps& tm_b, const GemmArgs& a,
                         int ctas, cudaStream_t stream) {
 #define MOE_CASE(G, N) \
   if (gemm_id == G && n_tile == N) return launch_one<G, N>(tm_w, tm_b, a, ctas, stream);

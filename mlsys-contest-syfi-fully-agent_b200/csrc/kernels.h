@@ -131,7 +131,14 @@ void launch_route_permute(const RouteArgs& r, const PermuteArgs& p, cudaStream_t
 void launch_route_only(const RouteArgs& r, cudaStream_t stream);
 void launch_gather_rows(const GatherArgs& a, int T, cudaStream_t stream);
 // gemm_id 1 or 2; n_tile in {16, 32, 64, 128}.  Returns a cudaError_t as int.
-int launch_grouped_gemm(int gemm_id, int n_tile, const CUtensorMap& tm_w, const CUtensorMap& tm_b, const GemmArgs& a,
+// Token-operand tensor maps of grouped_gemm_kernel: the same tensor with boxes of 1..4 row steps
+// (grouped_gemm_row_step(n_tile) rows each), so that a token tile with few valid rows (the last tile of an
+// expert, or an expert with a handful of tokens) brings only the rows it has, rounded up to a step.
+struct TokenMaps {
+  CUtensorMap m[4];
+};
+int grouped_gemm_row_step(int n_tile);   // rows per step: n_tile / 4 from 64-token tiles up, else 16
+int launch_grouped_gemm(int gemm_id, int n_tile, const CUtensorMap& tm_w, const TokenMaps& tm_b, const GemmArgs& a,
                         int ctas, cudaStream_t stream);
 constexpr int kFusedMaxTokens = 16;
 // Decode path in one launch: routing, GEMM1, SwiGLU, GEMM2 and combine (decode_kernel.cu).  `g` is the GEMM1 view

@@ -7,6 +7,7 @@
 #include <cuda.h>
 #include <cuda_runtime.h>
 
+#include <algorithm>
 #include <atomic>
 #include <cstdlib>
 #include <cstring>
@@ -100,12 +101,13 @@ struct MapKey {
     return true;
   }
 };
+constexpr int kMapCache = 64;   // a call uses up to 12 maps; several batch-size classes stay cached side by side
 struct MapEntry {
   MapKey key;
   CUtensorMap map;
   bool used;
 };
-MapEntry g_maps[32];
+MapEntry g_maps[kMapCache];
 int g_map_next = 0;
 
 int ensure_device(DeviceState** out) {
@@ -157,7 +159,7 @@ int get_map(DeviceState* d, const MapKey& key, CUtensorMap* out) {
     return MOE_B200_ECUDA;
   }
   MapEntry& e = g_maps[g_map_next];
-  g_map_next = (g_map_next + 1) % 32;
+  g_map_next = (g_map_next + 1) % kMapCache;
   e.key = key;
   e.map = m;
   e.used = true;
@@ -380,7 +382,16 @@ static int run_impl(const float* routing_logits, const uint16_t* routing_bias, c
     g_launches += 1;
     stage_mark(5, stream);
   } else {
-    if ((rc = launch_grouped_gemm(1, n_tile, tm_w13, tm_a, g1a, ctas, stream))) {
+    // token operands with boxes of 1..4 row steps (ragged token tiles bring only the rows they have)
+    TokenMaps tms_a, tms_c;
+    const int step1 = grouped_gemm_row_step(n_tile), step2 = grouped_gemm_row_step(n_tile2);
+    for (int i = 0; i < 4; ++i) {
+      const uint32_t r1 = static_cast<uint32_t>(std::min(n_tile, step1 * (i + 1)));
+      const uint32_t r2 = static_cast<uint32_t>(std::min(n_tile2, step2 * (i + 1)));
+      if ((rc = get_map(dev, kblock_map(a_packed, L.rows_cap, kH, r1, kps1), &tms_a.m[i]))) return rc;
+      if ((rc = get_map(dev, planes_map(cq, L.rows_cap, r2, kps2), &tms_c.m[i]))) return rc;
+    }
+    if ((rc = launch_grouped_gemm(1, n_tile, tm_w13, tms_a, g1a, ctas, stream))) {
       g_last_cuda_error = rc;
       return MOE_B200_ECUDA;
     }
@@ -393,7 +404,7 @@ static int run_impl(const float* routing_logits, const uint16_t* routing_bias, c
     g_launches += 1;
     stage_mark(4, stream);
 
-    if ((rc = launch_grouped_gemm(2, n_tile2, tm_w2, tm_c, g2a, ctas, stream))) {
+    if ((rc = launch_grouped_gemm(2, n_tile2, tm_w2, tms_c, g2a, ctas, stream))) {
       g_last_cuda_error = rc;
       return MOE_B200_ECUDA;
     }
