@@ -83,7 +83,9 @@ struct Cfg {
   static constexpr int CPW = N_TILE / 2;                                // token columns per epilogue warp
   static constexpr int CH = CPW > 64 ? 32 : CPW;                        // columns read back per tcgen05.ld batch
   static constexpr int STAGE_BYTES = KPS * KB_BYTES;
-  static constexpr int SC_BUFS = N_TILE <= 32 ? 2 : 1;                  // scale-product tables
+  // Scale-product tables.  With two, the next item's products are fetched during the current item's K loop;
+  // GEMM2's short items (16 K-blocks) on wide tiles measured faster with one table filled between two barriers.
+  static constexpr int SC_BUFS = (N_TILE <= 32 || (GEMM == 1 && !TOK_ON_M)) ? 2 : 1;
   static constexpr int SC_BYTES = SC_BUFS * KB * N_TILE * 4;
   static constexpr int AUX_BYTES = 1024;
   static constexpr int BUDGET = 227 * 1024 - 1024;   // 1 KB slack for the 1024-byte alignment of the ring
