@@ -54,7 +54,13 @@ size_t moe_fp8_block_scale_workspace_bytes(int T);
  * another stream (or process) that holds SMs for the whole call keeps some of its
  * CTAs from starting: the barrier waits then run out after 0.4 s and the call
  * ends with the error bits set (..._status returns MOE_B200_EKERNEL) -- no hang,
- * but no result either.  Keep decode-sized calls alone on the device. */
+ * but no result either.  Keep decode-sized calls alone on the device.
+ * CUDA graphs: the call may be recorded in a stream capture and replayed.  Everything
+ * that changes from call to call (the schedule, the decode kernel's barrier tag) lives
+ * in the workspace; tensor maps and addresses are baked into the recorded launches, so
+ * a replay uses the buffers of the capture.  Make one ordinary call with the same T on
+ * the device first (it sets the kernels' attributes), and do not switch
+ * ..._set_profiling on around a capture. */
 int moe_fp8_block_scale_run(const float* routing_logits, const uint16_t* routing_bias,
                             const uint8_t* hidden_states, const float* hidden_states_scale,
                             const uint8_t* gemm1_weights, const float* gemm1_weights_scale,

@@ -346,11 +346,19 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_w1, const __grid_constant__
   }
   griddep_wait();   // the workspace and the output belong to earlier launches until here
   unsigned int* bar = sched->bar1;
-  if (blockIdx.x == 0 && threadIdx.x == 0) grid_barrier_init(bar, a.g.call_tag);
+  unsigned int* epoch = sched->bar2;
+  // (the epoch is requested here and first used after the routing, so its latency is not waited for)
+  unsigned int tag_reg = 0;
+  if (threadIdx.x == 0) tag_reg = grid_barrier_next_tag(epoch);
   decode_route_schedule(a.g, smem, aux, fa, sched);
+  if (threadIdx.x == 0) {
+    aux->tag = tag_reg;
+    if (blockIdx.x == 0) grid_barrier_init(bar, tag_reg);
+  }
   tc_fence_before_sync();
   __syncthreads();
   tc_fence_after_sync();
+  const unsigned int call_tag = aux->tag;
   const int tiles = fa->tiles;
   const int n_sel_pad = fa->n_sel_pad;
   const uint32_t tmem_base = aux->tmem_base;
@@ -413,7 +421,7 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_w1, const __grid_constant__
                   }
                 }
               }
-              if (!grid_barrier_wait(bar, a.g.call_tag, 2 * n_ctas)) { *abort_flag = 1; ok = false; break; }
+              if (!grid_barrier_wait(bar, call_tag, 2 * n_ctas)) { *abort_flag = 1; ok = false; break; }
               fence_proxy_async_global();   // the planes were written with ordinary stores by other SMs
               ready = true;
             }
@@ -467,7 +475,7 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_w1, const __grid_constant__
     c.etid = threadIdx.x - kFirstEpiWarp * 32;
     constexpr int kEpiThreads = kEpiWarps * 32;
     // arrivals are only valid once CTA 0 has installed this launch's tag; checked here, long before the first one
-    if (c.etid == 0 && !grid_barrier_tag_wait(bar, a.g.call_tag)) *abort_flag = 1;
+    if (c.etid == 0 && !grid_barrier_tag_wait(bar, call_tag)) *abort_flag = 1;
 
     promote_items<1>(a, c, tiles, n_sel_pad, 0.0f);
 
@@ -490,7 +498,7 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_w1, const __grid_constant__
     c.sync();
     if (c.ok && c.etid == 0) {
       grid_barrier_arrive(bar);
-      if (!grid_barrier_wait(bar, a.g.call_tag, n_ctas)) *abort_flag = 1;
+      if (!grid_barrier_wait(bar, call_tag, n_ctas)) *abort_flag = 1;
     }
     c.sync();
     if (c.ok && !*abort_flag) {
@@ -526,7 +534,7 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_w1, const __grid_constant__
     c.sync();
     if (c.ok && c.etid == 0) {
       grid_barrier_arrive(bar);
-      if (!grid_barrier_wait(bar, a.g.call_tag, 2 * n_ctas)) *abort_flag = 1;
+      if (!grid_barrier_wait(bar, call_tag, 2 * n_ctas)) *abort_flag = 1;
     }
     c.sync();
 
@@ -536,7 +544,7 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_w1, const __grid_constant__
     c.sync();
     if (c.ok && c.etid == 0) {
       grid_barrier_arrive(bar);
-      if (!grid_barrier_wait(bar, a.g.call_tag, 3 * n_ctas)) *abort_flag = 1;
+      if (!grid_barrier_wait(bar, call_tag, 3 * n_ctas)) *abort_flag = 1;
     }
     c.sync();
     if (c.ok && !*abort_flag) {
@@ -564,6 +572,7 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_w1, const __grid_constant__
   tc_fence_before_sync();
   __syncthreads();
   if (threadIdx.x == 0 && aux->abort) atomicOr(&sched->status, kErrGemm1Timeout | kErrGemm2Timeout);
+  if (blockIdx.x == 0 && threadIdx.x == 0) *reinterpret_cast<volatile unsigned int*>(epoch) = call_tag;   // the next launch's tag differs
   if (warp == 1) {
     __syncwarp();
     tc_fence_after_sync();

@@ -30,6 +30,7 @@ struct Aux {
   int abort;
   int prefix[kELocal + 1];
   int offs[kELocal + 1];
+  unsigned int tag;        // decode kernel: this launch's grid-barrier tag
 };
 static_assert(sizeof(Aux) <= 1024, "Aux must fit its slot");
 
@@ -52,6 +53,18 @@ static_assert(sizeof(FusedAux) <= 4096, "FusedAux must fit its slot");
 // call's, then adds one, then waits for `n` arrivals.  So the word needs no initialisation by the
 // caller and no reset between calls, and an arrival is one atomic add.  Bounded like every other
 // wait here: false on timeout.
+//
+// The tag comes from the device, not from the host: an epoch word next to the barrier word.  Every CTA
+// reads it when the kernel starts (tag = epoch + 1) and CTA 0 stores the tag back as the new epoch when
+// it leaves, which it can only do after every CTA has read the old one (the last barrier needs all
+// arrivals) or after a timeout (the launch has failed by then).  A launch recorded in a CUDA graph and
+// replayed therefore tags every replay differently; a tag passed as a kernel argument would repeat.
+__device__ __forceinline__ unsigned int grid_barrier_next_tag(const unsigned int* epoch) {
+  unsigned int e;
+  asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(e) : "l"(epoch) : "memory");
+  return e + 1u;
+}
+
 __device__ __forceinline__ void grid_barrier_init(unsigned int* word2, unsigned int tag) {
   atomicExch(reinterpret_cast<unsigned long long*>(word2), static_cast<unsigned long long>(tag) << 32);
 }

@@ -91,7 +91,6 @@ struct GemmArgs {
   int T, local_expert_offset;
   float routed_scaling_factor;
   int ctas, rows_cap, slab_rows;
-  unsigned int call_tag;        // distinct per call: tags the grid barrier words
   int* topk_idx; float* topk_w; uint32_t* local_mask;
   int* perm_token; float* perm_weight; int* tok_rows;
   uint8_t* cq; float* c_scale;  // SwiGLU planes and their scales

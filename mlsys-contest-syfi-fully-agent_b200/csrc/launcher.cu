@@ -311,7 +311,6 @@ static int run_impl(const float* routing_logits, const uint16_t* routing_bias, c
   if (T <= kFusedMaxTokens) {
     // Decode path: one launch.  The kernel routes, reads the token rows straight from hidden_states (all
     // tokens are one token tile), and runs both GEMMs with the SwiGLU and combine phases in between and after.
-    static std::atomic<unsigned int> call_counter{0x9E3779B1u};
     CUtensorMap tm_h;
     if ((rc = get_map(dev, kblock_map(hidden_states, static_cast<uint64_t>(T), kH, kFusedMaxTokens, kps1), &tm_h)))
       return rc;
@@ -320,7 +319,6 @@ static int run_impl(const float* routing_logits, const uint16_t* routing_bias, c
     fa.logits = routing_logits; fa.bias_bf16 = routing_bias; fa.hidden_scale = hidden_states_scale;
     fa.T = T; fa.local_expert_offset = local_expert_offset; fa.routed_scaling_factor = routed_scaling_factor;
     fa.ctas = ctas; fa.rows_cap = L.rows_cap; fa.slab_rows = L.slab_rows;
-    fa.call_tag = call_counter.fetch_add(2654435761u) | 1u;
     fa.topk_idx = topk_idx; fa.topk_w = topk_w; fa.local_mask = local_mask;
     fa.perm_token = perm_token; fa.perm_weight = perm_weight; fa.tok_rows = tok_rows;
     fa.cq = cq; fa.c_scale = c_scale; fa.out_bf16 = output; fa.out_rows = output_rows;

@@ -48,7 +48,7 @@ struct MoeSched {
   int split1, split2;      // split-K factors chosen for GEMM1 / GEMM2 (0: balanced partition of the decode path)
   int items1, items2;      // work items of GEMM1 / GEMM2 (decode path: pipeline stages)
   unsigned int bar1[2];    // grid barrier of the decode kernel: {arrivals, call tag}
-  unsigned int bar2[2];    // spare
+  unsigned int bar2[2];    // [0]: epoch of the decode kernel's barrier tag (the last launch's tag); [1]: spare
   int n_tile2;             // token-tile width of GEMM2 (<= n_tile)
   int ctas;                // persistent CTAs of the launch that wrote this block (decode path; else 0)
   int counts[kELocal];

@@ -282,6 +282,36 @@ def test_host_buffer_entry_point(pkg, dev, W):
     assert torch.equal(out_h.view(torch.int16), want.view(torch.int16))
 
 
+@pytest.mark.parametrize("T", [1, 8, 64, 1100])
+def test_cuda_graph_replay(pkg, dev, W, T):
+    """The operator call recorded in a CUDA graph (after one ordinary call) and replayed over new values in the
+    same buffers gives the bits of ordinary calls, replay after replay: all launch state that changes from call
+    to call lives on the device (the decode kernel's barrier tag among it)."""
+    gen = pkg.gen
+    toks = [gen.make_tokens(T, seed, dev) for seed in (11, 12, 13)]
+    want = [run_op(pkg, t, W, 0).clone() for t in toks]
+    buf = gen.make_tokens(T, 11, dev)
+    out = torch.empty(T, 7168, dtype=torch.bfloat16, device=dev)
+    run_op(pkg, buf, W, 0, out=out)                      # sizes the workspace, fills the tensor-map cache
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        pkg.op.run(buf.routing_logits, buf.routing_bias, buf.hidden_states, buf.hidden_states_scale,
+                   W.gemm1_weights, W.gemm1_weights_scale, W.gemm2_weights, W.gemm2_weights_scale, 0, RSF, out)
+    for rep in range(2):
+        for t, w in zip(toks, want):
+            buf.routing_logits.copy_(t.routing_logits)
+            buf.routing_bias.copy_(t.routing_bias)
+            buf.hidden_states.view(torch.uint8).copy_(t.hidden_states.view(torch.uint8))
+            buf.hidden_states_scale.copy_(t.hidden_states_scale)
+            out.zero_()
+            graph.replay()
+            graph.replay()                               # back to back: the second replay meets the first one's barrier word
+            torch.cuda.synchronize()
+            assert pkg.op.kernel_status() == 0
+            assert torch.equal(out.view(torch.int16), w.view(torch.int16)), (T, rep)
+
+
 def test_workspace_too_small_is_reported(pkg, dev, W):
     tok = pkg.gen.make_tokens(8, 0, dev)
     out = torch.empty(8, 7168, dtype=torch.bfloat16, device=dev)
