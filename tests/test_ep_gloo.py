@@ -1,4 +1,4 @@
-"""CPU tests of the expert-parallel layer's host logic with gloo ranks (world size 2 and 4):
+"""CPU tests of the expert-parallel layer's host logic with gloo ranks (world size 2, 4 and 8):
 dispatch lists, count exchange, all-to-all plumbing and the ascending-shard combine.
 The shard operator is replaced by a cheap per-token stand-in with the operator's
 signature (the real one needs a GPU); routing is the oracle's."""
@@ -75,7 +75,7 @@ def _worker(rank, world, port, T_total, ret):
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("world", [2, 4])
+@pytest.mark.parametrize("world", [2, 4, 8])
 def test_expert_parallel_layer_matches_single_process_reference(world):
     port = _free_port()
     mgr = mp.Manager()
