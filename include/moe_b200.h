@@ -131,6 +131,21 @@ int moe_ep_dispatch_push(const uint8_t* hidden_states, const float* hidden_state
                          const float* routing_logits, int T, const int64_t* rec_token, int n_records,
                          const moe_ep_segment* segments, int n_segments, void* stream);
 
+/* Dispatch plan of one rank of the expert-parallel layer from its routing result topk_idx [T, 8] (global
+ * expert ids, 16-byte aligned): counts9[s] = records for shard s = 0..7 and counts9[8] = T; send_order /
+ * send_shard [sum of counts] = token and shard of every record, shard-major with ascending tokens inside a
+ * shard (capacity 8 T each); row_of [T, 8] = position of the record of (token, shard) in that order, -1 if
+ * the token selected no expert of the shard.  One kernel, no host synchronisation. */
+int moe_ep_plan(const int32_t* topk_idx, int T, int64_t* counts9, int64_t* send_order, int64_t* send_shard,
+                int32_t* row_of, void* stream);
+
+/* out_ptrs[r] for the n_rows result rows of a rank's shard operators (the output_rows argument of
+ * ..._run_rows): the rows come in up to eight runs, run k of run_count_host[k] consecutive rows whose
+ * destinations start at run_base_host[k] (a device address, possibly peer-mapped) and lie row_bytes apart.
+ * The two run arrays are HOST arrays; their counts must add up to n_rows. */
+int moe_ep_row_pointers(const int64_t* run_base_host, const int64_t* run_count_host, int n_runs, int64_t row_bytes,
+                        int64_t* out_ptrs, int n_rows, void* stream);
+
 /* Last step of the expert-parallel layer: output[t] = bf16(sum, in ascending shard order and in fp32, of the
  * bf16 rows back_rows[row_of[t][s]] for the shards s = 0..7 with row_of[t][s] >= 0).  The order and the
  * arithmetic are those in which the layer reference sums the eight shard outputs

@@ -95,10 +95,160 @@ __global__ void __launch_bounds__(224) ep_sum_shards_kernel(const uint16_t* __re
   static_assert(kChunks == 4 * 224, "row chunks per thread");
 }
 
+// Dispatch plan of one rank: which (token, shard) records it sends, shard-major with ascending tokens inside a
+// shard (the order torch.nonzero gives on the transposed hit mask), the per-shard counts, and for every
+// (token, shard) the position of its record in that order (-1: not selected).  One CTA: every thread owns a run
+// of consecutive tokens, counts its hits per shard, the CTA scans the counts, and the thread writes its records
+// at the scanned positions.  Replaces about twenty host-launched tensor operations and the host stop inside
+// torch.nonzero; the counts go to the peers without touching the host.
+constexpr int kPlanThreads = 1024;
+
+__device__ __forceinline__ uint32_t shard_mask_of(const int32_t* __restrict__ topk, int t) {
+  const int4 a = __ldg(reinterpret_cast<const int4*>(topk + static_cast<size_t>(t) * kTopK));
+  const int4 b = __ldg(reinterpret_cast<const int4*>(topk + static_cast<size_t>(t) * kTopK) + 1);
+  const int e[kTopK] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+  uint32_t m = 0;
+#pragma unroll
+  for (int k = 0; k < kTopK; ++k)
+    if (e[k] >= 0 && e[k] < kEGlobal) m |= 1u << (e[k] / kELocal);
+  return m;
+}
+
+__global__ void __launch_bounds__(kPlanThreads) ep_plan_kernel(const int32_t* __restrict__ topk, int T,
+                                                              int64_t* __restrict__ counts9,
+                                                              int64_t* __restrict__ send_order,
+                                                              int64_t* __restrict__ send_shard,
+                                                              int32_t* __restrict__ row_of) {
+  griddep_launch_dependents();
+  griddep_wait();
+  constexpr int kShards = kEGlobal / kELocal;   // 8
+  static_assert(kShards == 8 && kTopK == 8, "record layout");
+  __shared__ int warp_tot[kPlanThreads / 32][kShards];
+  __shared__ int warp_off[kPlanThreads / 32][kShards];
+  __shared__ int base[kShards];
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int chunk = (T + kPlanThreads - 1) / kPlanThreads;
+  const int t0 = min(T, tid * chunk), t1 = min(T, t0 + chunk);
+  int c[kShards];
+#pragma unroll
+  for (int s = 0; s < kShards; ++s) c[s] = 0;
+  for (int t = t0; t < t1; ++t) {
+    const uint32_t m = shard_mask_of(topk, t);
+#pragma unroll
+    for (int s = 0; s < kShards; ++s) c[s] += (m >> s) & 1u;
+  }
+  int excl[kShards];
+#pragma unroll
+  for (int s = 0; s < kShards; ++s) {
+    int v = c[s];
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) {
+      const int u = __shfl_up_sync(0xFFFFFFFFu, v, d);
+      if (lane >= d) v += u;
+    }
+    excl[s] = v - c[s];
+    if (lane == 31) warp_tot[warp][s] = v;
+  }
+  __syncthreads();
+  if (tid < kShards) {
+    int run = 0;
+    for (int w = 0; w < kPlanThreads / 32; ++w) {
+      warp_off[w][tid] = run;
+      run += warp_tot[w][tid];
+    }
+    base[tid] = run;      // the shard's total, turned into its start below
+  }
+  __syncthreads();
+  if (tid == 0) {
+    int b = 0;
+    for (int s = 0; s < kShards; ++s) {
+      const int n = base[s];
+      counts9[s] = n;
+      base[s] = b;
+      b += n;
+    }
+    counts9[kShards] = T;
+  }
+  __syncthreads();
+  int pos[kShards];
+#pragma unroll
+  for (int s = 0; s < kShards; ++s) pos[s] = base[s] + warp_off[warp][s] + excl[s];
+  for (int t = t0; t < t1; ++t) {
+    const uint32_t m = shard_mask_of(topk, t);
+#pragma unroll
+    for (int s = 0; s < kShards; ++s) {
+      int r = -1;
+      if ((m >> s) & 1u) {
+        r = pos[s]++;
+        send_order[r] = t;
+        send_shard[r] = s;
+      }
+      row_of[static_cast<size_t>(t) * kShards + s] = r;
+    }
+  }
+}
+
+// Destination address of every result row of this rank's shard operators: rows come in up to eight
+// runs (owned shard x source rank), run k holding count[k] consecutive rows whose destinations start at base[k]
+// and lie row_bytes apart.
+struct PtrRuns {
+  long long start[9];      // first row of run k (start[n] = total rows)
+  long long base[8];
+  int n;
+};
+
+__global__ void __launch_bounds__(256) ep_row_pointers_kernel(PtrRuns runs, long long row_bytes, int64_t* __restrict__ out,
+                                                              int n_rows) {
+  griddep_launch_dependents();
+  griddep_wait();
+  for (int r = blockIdx.x * blockDim.x + threadIdx.x; r < n_rows; r += gridDim.x * blockDim.x) {
+    int k = 0;
+#pragma unroll
+    for (int j = 1; j < 8; ++j)
+      if (j < runs.n && r >= runs.start[j]) k = j;
+    out[r] = runs.base[k] + (r - runs.start[k]) * row_bytes;
+  }
+}
+
 }  // namespace
 }  // namespace moe
 
 using namespace moe;
+
+extern "C" int moe_ep_row_pointers(const int64_t* run_base_host, const int64_t* run_count_host, int n_runs,
+                                   int64_t row_bytes, int64_t* out_ptrs, int n_rows, void* stream_v) {
+  if (n_runs < 0 || n_runs > 8 || n_rows < 0 || row_bytes <= 0) return MOE_B200_EINVAL;
+  if (n_rows == 0) return MOE_B200_OK;
+  if (!run_base_host || !run_count_host || !out_ptrs || n_runs == 0) return MOE_B200_EINVAL;
+  PtrRuns runs{};
+  long long pos = 0;
+  int n = 0;
+  for (int k = 0; k < n_runs; ++k) {
+    if (run_count_host[k] < 0) return MOE_B200_EINVAL;
+    if (run_count_host[k] == 0) continue;       // empty runs own no row
+    runs.start[n] = pos;
+    runs.base[n] = run_base_host[k];
+    pos += run_count_host[k];
+    ++n;
+  }
+  if (pos != n_rows) return MOE_B200_EINVAL;
+  runs.start[n] = pos;
+  runs.n = n;
+  const int blocks = (n_rows + 255) / 256 < 4 * kNumSMs ? (n_rows + 255) / 256 : 4 * kNumSMs;
+  cudaError_t e = launch_pdl(ep_row_pointers_kernel, dim3(blocks), dim3(256), 0, static_cast<cudaStream_t>(stream_v),
+                             runs, static_cast<long long>(row_bytes), out_ptrs, n_rows);
+  return e == cudaSuccess ? MOE_B200_OK : MOE_B200_ECUDA;
+}
+
+extern "C" int moe_ep_plan(const int32_t* topk_idx, int T, int64_t* counts9, int64_t* send_order, int64_t* send_shard,
+                           int32_t* row_of, void* stream_v) {
+  if (T < 0) return MOE_B200_EINVAL;
+  if (!counts9 || (T > 0 && (!topk_idx || !send_order || !send_shard || !row_of))) return MOE_B200_EINVAL;
+  if (reinterpret_cast<uintptr_t>(topk_idx) & 15u) return MOE_B200_EINVAL;
+  cudaError_t e = launch_pdl(ep_plan_kernel, dim3(1), dim3(kPlanThreads), 0, static_cast<cudaStream_t>(stream_v),
+                             topk_idx, T, counts9, send_order, send_shard, row_of);
+  return e == cudaSuccess ? MOE_B200_OK : MOE_B200_ECUDA;
+}
 
 extern "C" int moe_ep_dispatch_push(const uint8_t* hidden_states, const float* hidden_states_scale,
                                     const float* routing_logits, int T, const int64_t* rec_token, int n_records,

@@ -73,6 +73,7 @@ class DispatchPlan:
     send_order: torch.Tensor               # local token index of every sent row, in send-buffer order
     send_shard: torch.Tensor               # shard of every sent row (same order)
     tokens_per_rank: List[int]             # T_local of every rank (same table on every rank)
+    row_of: Optional[torch.Tensor] = None  # [T, 8] int32: position of (token, shard) in send order, -1 if absent
 
 
 def build_plan(topk_idx: torch.Tensor, world: int, rank: int, group=None) -> DispatchPlan:
@@ -80,6 +81,8 @@ def build_plan(topk_idx: torch.Tensor, world: int, rank: int, group=None) -> Dis
     the gathered [world, 9] table of per-shard counts and token counts."""
     dev = topk_idx.device
     T = topk_idx.shape[0]
+    if dev.type == "cuda" and topk_idx.dtype == torch.int32 and topk_idx.is_contiguous():
+        return _build_plan_device(topk_idx, world, rank, group)
     shard_of = (topk_idx.long() // E_LOCAL)                                   # [T, 8]
     hit = torch.zeros((T, N_SHARDS), dtype=torch.bool, device=dev)
     hit.scatter_(1, shard_of, True)
@@ -102,6 +105,41 @@ def build_plan(topk_idx: torch.Tensor, world: int, rank: int, group=None) -> Dis
                         pairs[:, 0].contiguous(), [int(x) for x in table[:, N_SHARDS]])
 
 
+def _build_plan_device(topk_idx: torch.Tensor, world: int, rank: int, group=None) -> DispatchPlan:
+    """``build_plan`` for a routing result on the GPU: one kernel (``moe_ep_plan``) makes the record order, the
+    counts and the (token, shard) -> record table; the counts are gathered on the device and cross to the host
+    once.  Same plan, element for element, as the tensor-operation path (compared in tests/test_gpu_ep.py)."""
+    from . import loader
+    dev = topk_idx.device
+    T = topk_idx.shape[0]
+    mine = torch.empty(N_SHARDS + 1, dtype=torch.int64, device=dev)
+    order = torch.empty(max(1, N_SHARDS * T), dtype=torch.int64, device=dev)
+    shard = torch.empty(max(1, N_SHARDS * T), dtype=torch.int64, device=dev)
+    row_of = torch.empty((T, N_SHARDS), dtype=torch.int32, device=dev)
+    with torch.cuda.device(dev):
+        loader.check(loader.lib.moe_ep_plan(topk_idx.data_ptr(), int(T), mine.data_ptr(), order.data_ptr(),
+                                            shard.data_ptr(), row_of.data_ptr(),
+                                            torch.cuda.current_stream(dev).cuda_stream))
+    if world > 1:
+        table_dev = torch.empty((world, N_SHARDS + 1), dtype=torch.int64, device=dev)
+        dist.all_gather_into_tensor(table_dev, mine, group=group)
+    else:
+        table_dev = mine.view(1, -1)
+    table = table_dev.cpu()                                                   # the call's one host synchronisation
+    counts = table[:, :N_SHARDS].contiguous()
+    own = counts[rank].tolist()
+    bounds = [0]
+    for c in own:
+        bounds.append(bounds[-1] + c)
+    send_order, send_shard = order[:bounds[-1]], shard[:bounds[-1]]
+    token_lists = [send_order[bounds[s]:bounds[s + 1]] for s in range(N_SHARDS)]
+    per = N_SHARDS // world
+    send_counts = [sum(own[d * per:(d + 1) * per]) for d in range(world)]
+    recv_counts = [int(counts[src, rank * per:(rank + 1) * per].sum()) for src in range(world)]
+    return DispatchPlan(token_lists, send_counts, recv_counts, counts, send_order, send_shard,
+                        [int(x) for x in table[:, N_SHARDS]], row_of)
+
+
 def sum_shards(plan: DispatchPlan, back: torch.Tensor, T: int) -> torch.Tensor:
     """Layer output of this rank's tokens from the returned rows (send order: shard-major, ascending token):
     fp32 sum in ascending shard order, one bf16 rounding.  On a GPU this is one kernel
@@ -109,10 +147,12 @@ def sum_shards(plan: DispatchPlan, back: torch.Tensor, T: int) -> torch.Tensor:
     dev = back.device
     if dev.type == "cuda":
         from . import loader
-        row_of = torch.full((T, N_SHARDS), -1, dtype=torch.int32, device=dev)
-        n = int(plan.send_order.numel())
-        if n:       # send order is shard-major: row i of `back` belongs to (send_order[i], send_shard[i])
-            row_of[plan.send_order, plan.send_shard] = torch.arange(n, dtype=torch.int32, device=dev)
+        row_of = plan.row_of
+        if row_of is None:
+            row_of = torch.full((T, N_SHARDS), -1, dtype=torch.int32, device=dev)
+            n = int(plan.send_order.numel())
+            if n:   # send order is shard-major: row i of `back` belongs to (send_order[i], send_shard[i])
+                row_of[plan.send_order, plan.send_shard] = torch.arange(n, dtype=torch.int32, device=dev)
         out = torch.empty((T, H), dtype=torch.bfloat16, device=dev)
         back = back.contiguous()
         with torch.cuda.device(dev):
@@ -321,8 +361,8 @@ def _forward_p2p(self, plan: DispatchPlan, routing_logits, routing_bias, hidden_
                 hidden_states.data_ptr(), hidden_states_scale.data_ptr(), routing_logits.data_ptr(), int(T),
                 plan.send_order.data_ptr(), n_send, segs, nseg, torch.cuda.current_stream(dev).cuda_stream))
     # Destination of every result row, for all of this rank's shards at once (receive-area order: shard-major,
-    # then source rank): the position of the row's record in the source rank's send order.  A handful of
-    # device operations on one small host table instead of a Python loop per (source, shard).
+    # then source rank): the position of the row's record in the source rank's send order.  One small kernel
+    # (moe_ep_row_pointers) from the eight (owned shard, source rank) runs.
     ptr_table = None
     if n_recv:
         seg_base, seg_cnt = [], []
@@ -330,11 +370,13 @@ def _forward_p2p(self, plan: DispatchPlan, routing_logits, routing_bias, hidden_
             for src in range(world):
                 seg_base.append(px.ptrs[src] + px.off_back + int(counts[src, :s].sum()) * H * 2)
                 seg_cnt.append(int(counts[src, s]))
-        host = torch.tensor([seg_base, seg_cnt], dtype=torch.int64).pin_memory()
-        seg = host.to(dev, non_blocking=True)
-        seg_id = torch.repeat_interleave(torch.arange(seg.shape[1], device=dev), seg[1], output_size=n_recv)
-        start = torch.cumsum(seg[1], 0) - seg[1]
-        ptr_table = seg[0][seg_id] + (torch.arange(n_recv, device=dev) - start[seg_id]) * (H * 2)
+        nseg = len(seg_base)
+        base_arr = (ctypes.c_int64 * nseg)(*seg_base)
+        cnt_arr = (ctypes.c_int64 * nseg)(*seg_cnt)
+        ptr_table = torch.empty(n_recv, dtype=torch.int64, device=dev)
+        with torch.cuda.device(dev):
+            loader.check(loader.lib.moe_ep_row_pointers(base_arr, cnt_arr, nseg, H * 2, ptr_table.data_ptr(), n_recv,
+                                                        torch.cuda.current_stream(dev).cuda_stream))
     px.barrier()                                            # every record has landed
 
     recv_h, recv_s, recv_l = px.recv_views(n_recv)

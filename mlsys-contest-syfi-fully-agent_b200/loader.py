@@ -34,6 +34,8 @@ EXPORTS = [
     "moe_fp8_block_scale_get_options",
     "moe_ep_dispatch_push",
     "moe_ep_sum_shards",
+    "moe_ep_plan",
+    "moe_ep_row_pointers",
 ]
 STATIC_MAX_TOKENS = 4096
 STAGES = ("route_permute", "gather", "gemm1", "swiglu_split", "gemm2", "combine")
@@ -99,6 +101,10 @@ def _load() -> ctypes.CDLL:
     lib.moe_ep_dispatch_push.argtypes = [vp, vp, vp, i32, vp, i32, ctypes.POINTER(EpSegment), i32, vp]
     lib.moe_ep_sum_shards.restype = i32
     lib.moe_ep_sum_shards.argtypes = [vp, vp, i32, vp, vp]
+    lib.moe_ep_plan.restype = i32
+    lib.moe_ep_plan.argtypes = [vp, i32, vp, vp, vp, vp, vp]
+    lib.moe_ep_row_pointers.restype = i32
+    lib.moe_ep_row_pointers.argtypes = [vp, vp, i32, ctypes.c_int64, vp, i32, vp]
     lib.moe_fp8_block_scale_set_options.restype = i32
     lib.moe_fp8_block_scale_set_options.argtypes = [ctypes.c_uint]
     lib.moe_fp8_block_scale_get_options.restype = ctypes.c_uint

@@ -53,6 +53,29 @@ def _layer_case(pkg, rank, world, dev, transport="nccl"):
     return m
 
 
+@pytest.mark.parametrize("T", [1, 7, 64, 1000, 2048, 5000])
+def test_plan_kernel_matches_tensor_operation_plan(pkg, T):
+    """moe_ep_plan (one kernel, no host stop before the count table) against the torch.nonzero construction:
+    the same records in the same order, the same counts, and row_of consistent with them."""
+    ep, gen, op = pkg.ep, pkg.gen, pkg.op
+    dev = torch.device("cuda", 0)
+    tok = gen.make_tokens(T, 40 + T, dev, skew=(T % 2 == 0))
+    topk = op.route(tok.routing_logits, tok.routing_bias, 0, RSF)[0]
+    assert topk.dtype == torch.int32
+    fast = ep.build_plan(topk, 1, 0)
+    slow = ep.build_plan(topk.long(), 1, 0)          # int64 indices take the tensor-operation path
+    assert fast.row_of is not None and slow.row_of is None
+    assert torch.equal(fast.counts, slow.counts) and fast.tokens_per_rank == slow.tokens_per_rank == [T]
+    assert fast.send_counts == slow.send_counts and fast.recv_counts == slow.recv_counts
+    assert torch.equal(fast.send_order, slow.send_order) and torch.equal(fast.send_shard, slow.send_shard)
+    for a, b in zip(fast.token_lists, slow.token_lists):
+        assert torch.equal(a, b)
+    n = int(fast.send_order.numel())
+    want = torch.full((T, 8), -1, dtype=torch.int32, device=dev)
+    want[slow.send_order, slow.send_shard] = torch.arange(n, dtype=torch.int32, device=dev)
+    assert torch.equal(fast.row_of, want)
+
+
 def _check(m):
     assert m["cosine"] >= 0.9999, m
     # each shard output is already within the operator's bar; the layer adds <= 4 of them
