@@ -640,6 +640,28 @@ def bench_ep(args):
     if len(results) == 2:
         assert results["p2p"]["digest"] == results["nccl"]["digest"], "transports disagree"
 
+    # ---- the same layer from bf16 activations: the dispatch kernel quantises every token on its way out.  The bf16
+    # rows are the ones the generator quantised into `hidden`, so the output must have the same bits.
+    bf16_dispatch = None
+    if transports[0] == "p2p":
+        x_all = gen.normal(0, gen._S_HIDDEN, 0, EP_T * H, dev).view(EP_T, H).to(torch.bfloat16)
+        x = x_all[sl].contiguous()
+        del x_all
+        layer = ep.ExpertParallelMoE(weights, rank, world, transport="p2p")
+        for _ in range(args.warmup):
+            out_b = layer.forward_bf16(logits, bias, x, RSF)
+        sync()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(args.steps):
+            out_b = layer.forward_bf16(logits, bias, x, RSF)
+        e1.record()
+        sync()
+        assert gen.digest(out_b) == results["p2p"]["digest"], "bf16 dispatch changed the result"
+        bf16_dispatch = {"ms_per_step": max_over_ranks(e0.elapsed_time(e1)) / args.steps,
+                         "note": "activations enter as bf16; quantise + pack + send in one kernel; bit-identical output"}
+        del layer, x, out_b
+
     # ---- parity of the layer output against the oracle (every rank, its own tokens)
     rep = layer_parity(oracle, ep, tok_all, weights, shards, world, outs[transports[0]], sl)
     check_layer_parity(rep)
@@ -740,6 +762,7 @@ def bench_ep(args):
                 "load_balance_bound": total_rows / world / rows_max},
             "gpu_launches": int(head["launches"]),
             "clocks": clocks,
+            "bf16_dispatch": bf16_dispatch,
             "nccl_transport": ({"ms_per_step": results["nccl"]["ms_step"],
                                 "tokens_per_s": EP_T / (results["nccl"]["ms_step"] * 1e-3)}
                                if "nccl" in results and transports[0] != "nccl" else None),

@@ -131,6 +131,14 @@ int moe_ep_dispatch_push(const uint8_t* hidden_states, const float* hidden_state
                          const float* routing_logits, int T, const int64_t* rec_token, int n_records,
                          const moe_ep_segment* segments, int n_segments, void* stream);
 
+/* The same dispatch for activations that are still bf16 [T, 7168] (8-byte aligned): every token is quantised
+ * once (the arithmetic of ..._quantize_activations, bit for bit) and its e4m3 row, 56 scales and logits are
+ * stored to every shard it selected.  segments_by_shard has EIGHT entries indexed by shard (count 0: none);
+ * row_of [T, 8] is the table ..._plan leaves: the record of (t, s) goes to position
+ * row_of[t][s] - segments_by_shard[s].first_record of the segment. */
+int moe_ep_quantize_push(const uint16_t* hidden_bf16, const float* routing_logits, int T, const int32_t* row_of,
+                         const moe_ep_segment* segments_by_shard, void* stream);
+
 /* Dispatch plan of one rank of the expert-parallel layer from its routing result topk_idx [T, 8] (global
  * expert ids, 16-byte aligned): counts9[s] = records for shard s = 0..7 and counts9[8] = T; send_order /
  * send_shard [sum of counts] = token and shard of every record, shard-major with ascending tokens inside a

@@ -11,6 +11,8 @@
 // Records are grouped in up to 8 segments (one per destination shard, ascending token inside);
 // `seg` tells where each segment starts in `rec_token`, how long it is, and the base addresses
 // of its three destination arrays at the owner.
+#include <cuda_fp8.h>
+
 #include "../../include/moe_b200.h"
 #include "kernels.h"
 
@@ -48,6 +50,79 @@ __global__ void __launch_bounds__(128) ep_dispatch_push_kernel(const uint8_t* __
     if (threadIdx.x >= 64 && threadIdx.x < 64 + kKB1)
       sg.dst_scale[k * kKB1 + (threadIdx.x - 64)] = __ldg(hidden_scale + static_cast<size_t>(threadIdx.x - 64) * T + t);
   }
+}
+
+// Quantise, pack and send in one pass: the dispatch for activations that are still bf16.  One CTA per token
+// quantises the row exactly as quantize_1x128_kernel does (scale = max(|x|, 1e-10) / 448 with IEEE division,
+// e4m3 round-to-nearest-even saturating; one warp per 128-column block, eight blocks per warp), keeps the 7168
+// bytes and 56 scales in shared memory, and stores them together with the token's logits to every shard the token
+// selected: the record's place at the owner is its position among the rank's records for that shard
+// (row_of[t][s] - first_record of the shard's segment).  The row is read from HBM once however many shards it
+// goes to, and the fp8 copy never exists in this rank's memory.
+struct SegByShard {
+  moe_ep_segment seg[8];      // indexed by shard; count == 0: no record for that shard
+};
+
+constexpr int kQPushThreads = 224;   // 7 warps x 8 blocks = 56 blocks; 448 16-byte chunks = 2 per thread
+
+__global__ void __launch_bounds__(kQPushThreads) ep_quantize_push_kernel(const uint16_t* __restrict__ x_bf16,
+                                                                        const float* __restrict__ logits, int T,
+                                                                        const int32_t* __restrict__ row_of,
+                                                                        SegByShard tab) {
+  griddep_launch_dependents();
+  griddep_wait();
+  __shared__ __align__(16) uint8_t q[kH];
+  __shared__ float sc[kKB1];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  for (int t = blockIdx.x; t < T; t += gridDim.x) {
+    int dest[8];
+    bool any = false;
+#pragma unroll
+    for (int s = 0; s < 8; ++s) {
+      dest[s] = __ldg(row_of + static_cast<size_t>(t) * 8 + s);
+      any |= dest[s] >= 0;
+    }
+    if (!any) continue;      // (uniform over the CTA)
+    for (int kb = warp; kb < kKB1; kb += kQPushThreads / 32) {
+      const size_t off = static_cast<size_t>(t) * kH + kb * kBlock + lane * 4;
+      const uint2 raw = __ldg(reinterpret_cast<const uint2*>(x_bf16 + off));
+      float v[4];
+      v[0] = __uint_as_float(raw.x << 16);
+      v[1] = __uint_as_float(raw.x & 0xFFFF0000u);
+      v[2] = __uint_as_float(raw.y << 16);
+      v[3] = __uint_as_float(raw.y & 0xFFFF0000u);
+      float amax = fmaxf(fmaxf(fabsf(v[0]), fabsf(v[1])), fmaxf(fabsf(v[2]), fabsf(v[3])));
+#pragma unroll
+      for (int d = 16; d > 0; d >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, d));
+      const float scale = __fdiv_rn(fmaxf(amax, 1e-10f), 448.0f);
+      uint32_t packed = 0;
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+        packed |= static_cast<uint32_t>(__nv_cvt_float_to_fp8(__fdiv_rn(v[i], scale), __NV_SATFINITE, __NV_E4M3)) << (8 * i);
+      *reinterpret_cast<uint32_t*>(q + kb * kBlock + lane * 4) = packed;
+      if (lane == 0) sc[kb] = scale;
+    }
+    __syncthreads();
+    const uint4 row0 = reinterpret_cast<const uint4*>(q)[threadIdx.x];
+    const uint4 row1 = reinterpret_cast<const uint4*>(q)[threadIdx.x + kQPushThreads];
+    uint4 lg = make_uint4(0u, 0u, 0u, 0u);
+    if (threadIdx.x < kEGlobal * 4 / 16)
+      lg = __ldg(reinterpret_cast<const uint4*>(logits + static_cast<size_t>(t) * kEGlobal) + threadIdx.x);
+    const float my_scale = threadIdx.x >= 64 && threadIdx.x < 64 + kKB1 ? sc[threadIdx.x - 64] : 0.0f;
+#pragma unroll
+    for (int s = 0; s < 8; ++s) {
+      if (dest[s] < 0) continue;
+      const moe_ep_segment sg = tab.seg[s];
+      const long long k = dest[s] - sg.first_record;
+      uint4* dst_h = reinterpret_cast<uint4*>(sg.dst_hidden + k * kH);
+      dst_h[threadIdx.x] = row0;
+      dst_h[threadIdx.x + kQPushThreads] = row1;
+      if (threadIdx.x < kEGlobal * 4 / 16) reinterpret_cast<uint4*>(sg.dst_logits + k * kEGlobal)[threadIdx.x] = lg;
+      if (threadIdx.x >= 64 && threadIdx.x < 64 + kKB1) sg.dst_scale[k * kKB1 + (threadIdx.x - 64)] = my_scale;
+    }
+    __syncthreads();      // the row buffer is reused by the next token
+  }
+  static_assert(kH / 16 == 2 * kQPushThreads && kKB1 == 8 * (kQPushThreads / 32), "chunks and blocks per thread");
 }
 
 // Final accumulation of the expert-parallel layer: out[t] = bf16(sum over shards s = 0..7, ascending, of
@@ -268,6 +343,30 @@ extern "C" int moe_ep_dispatch_push(const uint8_t* hidden_states, const float* h
   int blocks = n_records < 8 * kNumSMs ? n_records : 8 * kNumSMs;
   cudaError_t e = launch_pdl(ep_dispatch_push_kernel, dim3(blocks), dim3(128), 0, static_cast<cudaStream_t>(stream_v),
                              hidden_states, hidden_states_scale, routing_logits, T, rec_token, n_records, tab);
+  return e == cudaSuccess ? MOE_B200_OK : MOE_B200_ECUDA;
+}
+
+extern "C" int moe_ep_quantize_push(const uint16_t* hidden_bf16, const float* routing_logits, int T,
+                                    const int32_t* row_of, const moe_ep_segment* segments_by_shard, void* stream_v) {
+  if (T < 0) return MOE_B200_EINVAL;
+  if (T == 0) return MOE_B200_OK;
+  if (!hidden_bf16 || !routing_logits || !row_of || !segments_by_shard) return MOE_B200_EINVAL;
+  if ((reinterpret_cast<uintptr_t>(hidden_bf16) & 7u) || (reinterpret_cast<uintptr_t>(routing_logits) & 15u))
+    return MOE_B200_EINVAL;
+  SegByShard tab{};
+  for (int s = 0; s < 8; ++s) {
+    tab.seg[s] = segments_by_shard[s];
+    if (segments_by_shard[s].count < 0) return MOE_B200_EINVAL;
+    if (segments_by_shard[s].count == 0) continue;
+    if (!segments_by_shard[s].dst_hidden || !segments_by_shard[s].dst_scale || !segments_by_shard[s].dst_logits)
+      return MOE_B200_EINVAL;
+    if ((reinterpret_cast<uintptr_t>(segments_by_shard[s].dst_hidden) |
+         reinterpret_cast<uintptr_t>(segments_by_shard[s].dst_logits)) & 15u)
+      return MOE_B200_EINVAL;
+  }
+  const int blocks = T < 8 * kNumSMs ? T : 8 * kNumSMs;
+  cudaError_t e = launch_pdl(ep_quantize_push_kernel, dim3(blocks), dim3(kQPushThreads), 0,
+                             static_cast<cudaStream_t>(stream_v), hidden_bf16, routing_logits, T, row_of, tab);
   return e == cudaSuccess ? MOE_B200_OK : MOE_B200_ECUDA;
 }
 

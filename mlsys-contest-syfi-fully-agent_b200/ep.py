@@ -309,15 +309,37 @@ class ExpertParallelMoE:
         return sum_shards(plan, back, T)
 
 
+def _forward_bf16(self, routing_logits, routing_bias, hidden_bf16, routed_scaling_factor: float) -> torch.Tensor:
+    """The layer for activations that are still bf16 ``[T_local, 7168]``.  The p2p transport quantises every token
+    inside the dispatch kernel (quantise + pack + send in one pass, ``moe_ep_quantize_push``); the nccl transport
+    quantises first.  Bit-identical to ``forward`` on ``op.quantize_activations(hidden_bf16)``."""
+    if hidden_bf16.dtype != torch.bfloat16 or hidden_bf16.dim() != 2 or hidden_bf16.shape[1] != H or \
+            not hidden_bf16.is_contiguous():
+        raise ValueError("hidden_bf16 must be a contiguous bfloat16 [T, 7168]")
+    if self.transport != "p2p":
+        from . import op
+        q, sc = op.quantize_activations(hidden_bf16)
+        return self.forward(routing_logits, routing_bias, q, sc, routed_scaling_factor)
+    topk_idx = self.route_fn(routing_logits, routing_bias, routed_scaling_factor)
+    plan = build_plan(topk_idx, self.world, self.rank, self.group)
+    self.last_plan = plan
+    return self._forward_p2p(plan, routing_logits, routing_bias, None, None, routed_scaling_factor,
+                             hidden_bf16=hidden_bf16)
+
+
+ExpertParallelMoE.forward_bf16 = _forward_bf16
+
+
 def _forward_p2p(self, plan: DispatchPlan, routing_logits, routing_bias, hidden_states, hidden_states_scale,
-                 routed_scaling_factor: float) -> torch.Tensor:
-    """p2p transport: dispatch by one push kernel, combine inside the shard operator (see module docstring)."""
+                 routed_scaling_factor: float, hidden_bf16: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """p2p transport: dispatch by one push kernel, combine inside the shard operator (see module docstring).
+    With ``hidden_bf16`` (and no fp8 tensors) the dispatch kernel quantises each token on its way out."""
     import ctypes
 
     from . import loader, op
     world, rank = self.world, self.rank
     T = routing_logits.shape[0]
-    dev = hidden_states.device
+    dev = routing_logits.device
     n_logits = routing_logits.shape[1]
     per = N_SHARDS // world
     counts = plan.counts                                    # [world, 8] host, identical on every rank
@@ -343,7 +365,8 @@ def _forward_p2p(self, plan: DispatchPlan, routing_logits, routing_bias, hidden_
         return int(totals[first:s].sum()) + int(counts[:src, s].sum())
 
     px.barrier()                                            # peers have finished reading the previous call's areas
-    segs = (loader.EpSegment * N_SHARDS)()
+    segs = (loader.EpSegment * N_SHARDS)()                   # the non-empty segments, packed
+    by_shard = (loader.EpSegment * N_SHARDS)()               # the same, indexed by shard (count 0: none)
     nseg, first = 0, 0
     for s in range(N_SHARDS):
         n = int(counts[rank, s])
@@ -353,13 +376,21 @@ def _forward_p2p(self, plan: DispatchPlan, routing_logits, routing_bias, hidden_
             segs[nseg] = loader.EpSegment(first, n, px.ptrs[d] + px.off_h + row * H,
                                           px.ptrs[d] + px.off_s + row * KB * 4,
                                           px.ptrs[d] + px.off_l + row * n_logits * 4)
+            by_shard[s] = segs[nseg]
             nseg += 1
         first += n
     if n_send:
         with torch.cuda.device(dev):
-            loader.check(loader.lib.moe_ep_dispatch_push(
-                hidden_states.data_ptr(), hidden_states_scale.data_ptr(), routing_logits.data_ptr(), int(T),
-                plan.send_order.data_ptr(), n_send, segs, nseg, torch.cuda.current_stream(dev).cuda_stream))
+            stream = torch.cuda.current_stream(dev).cuda_stream
+            if hidden_bf16 is not None:
+                if plan.row_of is None:
+                    raise ValueError("the bf16 dispatch needs the device-side plan (int32 routing result on the GPU)")
+                loader.check(loader.lib.moe_ep_quantize_push(hidden_bf16.data_ptr(), routing_logits.data_ptr(), int(T),
+                                                             plan.row_of.data_ptr(), by_shard, stream))
+            else:
+                loader.check(loader.lib.moe_ep_dispatch_push(
+                    hidden_states.data_ptr(), hidden_states_scale.data_ptr(), routing_logits.data_ptr(), int(T),
+                    plan.send_order.data_ptr(), n_send, segs, nseg, stream))
     # Destination of every result row, for all of this rank's shards at once (receive-area order: shard-major,
     # then source rank): the position of the row's record in the source rank's send order.  One small kernel
     # (moe_ep_row_pointers) from the eight (owned shard, source rank) runs.

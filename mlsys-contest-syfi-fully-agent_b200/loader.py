@@ -36,6 +36,7 @@ EXPORTS = [
     "moe_ep_sum_shards",
     "moe_ep_plan",
     "moe_ep_row_pointers",
+    "moe_ep_quantize_push",
 ]
 STATIC_MAX_TOKENS = 4096
 STAGES = ("route_permute", "gather", "gemm1", "swiglu_split", "gemm2", "combine")
@@ -103,6 +104,8 @@ def _load() -> ctypes.CDLL:
     lib.moe_ep_sum_shards.argtypes = [vp, vp, i32, vp, vp]
     lib.moe_ep_plan.restype = i32
     lib.moe_ep_plan.argtypes = [vp, i32, vp, vp, vp, vp, vp]
+    lib.moe_ep_quantize_push.restype = i32
+    lib.moe_ep_quantize_push.argtypes = [vp, vp, i32, vp, ctypes.POINTER(EpSegment), vp]
     lib.moe_ep_row_pointers.restype = i32
     lib.moe_ep_row_pointers.argtypes = [vp, vp, i32, ctypes.c_int64, vp, i32, vp]
     lib.moe_fp8_block_scale_set_options.restype = i32

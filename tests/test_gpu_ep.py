@@ -76,6 +76,26 @@ def test_plan_kernel_matches_tensor_operation_plan(pkg, T):
     assert torch.equal(fast.row_of, want)
 
 
+def test_bf16_dispatch_quantises_on_the_way_out(pkg):
+    """forward_bf16 (quantise + pack + send in one kernel) against forward on separately quantised activations:
+    the same bits, on batches where tokens go to between one and several shards and some shards get nothing."""
+    ep, gen, op = pkg.ep, pkg.gen, pkg.op
+    dev = torch.device("cuda", 0)
+    weights = [gen.make_shard_weights(1000 + s, dev, experts=range(0, 32, 5)) for s in range(8)]
+    layer = ep.ExpertParallelMoE(weights, 0, 1, transport="p2p")
+    for T, seed, skew in ((1, 3, False), (33, 4, True), (700, 5, False)):
+        tok = gen.make_tokens(T, seed, dev, skew)
+        x = (gen.normal(seed, 77, 0, T * 7168, dev).view(T, 7168) * 3.0).to(torch.bfloat16).contiguous()
+        q, sc = op.quantize_activations(x)
+        want = layer.forward(tok.routing_logits, tok.routing_bias, q, sc, RSF)
+        got = layer.forward_bf16(tok.routing_logits, tok.routing_bias, x, RSF)
+        assert op.kernel_status(device=dev) == 0
+        assert torch.equal(got.view(torch.int16), want.view(torch.int16)), T
+        assert float(want.float().abs().max()) > 0.0
+    with pytest.raises(ValueError):
+        layer.forward_bf16(tok.routing_logits, tok.routing_bias, x.float(), RSF)
+
+
 def _check(m):
     assert m["cosine"] >= 0.9999, m
     # each shard output is already within the operator's bar; the layer adds <= 4 of them
