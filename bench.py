@@ -2,6 +2,8 @@
 """Benchmark of the FP8 block-scale DeepSeek-V3 MoE shard on B200.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload NAME]
+    python bench.py --replay ROOT|synthetic      # a flashinfer-trace workload set, per-workload table
+    python bench.py --profile-only --workload NAME   # W + K bare calls on one weight replica (profiler captures)
 
 One step = one call of the operator on one batch of seeded synthetic tokens.
 N = 1 measures the decode workload (T = 1, the configuration the headline metric
@@ -113,7 +115,7 @@ class ClockSampler:
               "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
 
     def __init__(self, index: int):
-        self.index, self.lines, self.proc = index, [], None
+        self.index, self.lines, self.proc, self.first = index, [], None, 0
 
     def __enter__(self):
         try:
@@ -122,6 +124,12 @@ class ClockSampler:
                  "-i", str(self.index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.thread = threading.Thread(target=self._read, daemon=True)
             self.thread.start()
+            # nvidia-smi needs a few hundred ms before its first line (longer on an 8-GPU box); a short timed
+            # region would otherwise end without a sample.  Wait for the first line, then count from there.
+            t0 = time.time()
+            while not self.lines and time.time() - t0 < 5.0:
+                time.sleep(0.005)
+            self.first = len(self.lines)
         except Exception:
             self.proc = None
         return self
@@ -132,7 +140,7 @@ class ClockSampler:
 
     def __exit__(self, *exc):
         if self.proc is not None:
-            time.sleep(0.15)
+            time.sleep(0.03)
             self.proc.terminate()
             try:
                 self.proc.wait(timeout=2)
@@ -142,7 +150,8 @@ class ClockSampler:
     def summary(self):
         sm, mx, reasons = [], [], set()
         names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
-        for ln in self.lines:
+        lines = self.lines[self.first:] or self.lines       # samples taken after the region began (else: all)
+        for ln in lines:
             parts = [p.strip() for p in ln.split(",")]
             if len(parts) < 6:
                 continue

@@ -364,7 +364,10 @@ def _forward_p2p(self, plan: DispatchPlan, routing_logits, routing_bias, hidden_
         first = d * per
         return int(totals[first:s].sum()) + int(counts[:src, s].sum())
 
-    px.barrier()                                            # peers have finished reading the previous call's areas
+    # No barrier is needed before the push.  The receive areas it overwrites were last read by the owners' shard
+    # operators of the previous call, and every rank passed that call's exit barrier only after its own shard
+    # operators (stream order); the back areas the shard operators of this call overwrite are read by the sources'
+    # final sums of the previous call, which precede this call's entry barrier below in each source's stream.
     segs = (loader.EpSegment * N_SHARDS)()                   # the non-empty segments, packed
     by_shard = (loader.EpSegment * N_SHARDS)()               # the same, indexed by shard (count 0: none)
     nseg, first = 0, 0
