@@ -48,7 +48,7 @@ UNIT = "tokens/s"
 RSF = 2.5
 H = 7168
 
-# single-GPU workloads (BASELINE.json configs 1, 0, 2, 3 and two sizes in between)
+# single-GPU workloads (the benchmark specification's configs 1, 0, 2, 3 and two sizes in between)
 WORKLOADS = {
     "decode_t1":     dict(T=1, token_seed=3, skew=False),    # seed 3: first seed whose token has a local expert
     "cpu_ref_t8":    dict(T=8, token_seed=0, skew=False),
@@ -57,7 +57,7 @@ WORKLOADS = {
     "mid_t512":      dict(T=512, token_seed=0, skew=False),
     "prefill_t4096": dict(T=4096, token_seed=0, skew=False),
 }
-EP_T = 16384                  # tokens of the expert-parallel layer workload (BASELINE.json config 4)
+EP_T = 16384                  # tokens of the expert-parallel layer workload (the specification's config 4)
 EP_REFERENCE_SAMPLE = 4       # tokens of it that the CPU arm pushes through all 256 experts per step
 
 # dram__bytes_read.sum + dram__bytes_write.sum of one launch of the dominant kernel, from ncu captures of the
@@ -504,7 +504,7 @@ def bench_single(args):
 
 
 # ---------------------------------------------------------------------------------------------
-# The 256-expert layer (BASELINE.json config 4): one GPU (scale anchor) and N > 1 under torchrun
+# The 256-expert layer (the specification's config 4): one GPU (scale anchor) and N > 1 under torchrun
 # ---------------------------------------------------------------------------------------------
 def layer_parity(oracle, ep, tok_all, weights, shards, world, out, sl):
     """This rank's rows of the layer output against the layer reference: every rank runs the oracle on the GPU

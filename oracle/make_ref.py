@@ -31,7 +31,7 @@ import subprocess
 HERE = os.path.dirname(os.path.abspath(__file__))
 DEST_DIR = os.path.join(HERE, "_ref")
 DEST = os.path.join(DEST_DIR, "moe_definition.py")
-DEFAULT_REFERENCE = "/root/reference"
+DEFAULT_REFERENCE = os.environ.get("MOE_REFERENCE_ROOT", "/root/reference")   # checkout of the reference repository
 
 
 def make_ref(reference: str = DEFAULT_REFERENCE):
