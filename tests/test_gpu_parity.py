@@ -153,6 +153,24 @@ def test_against_oracle(pkg, dev, W, T, seed, skew, offset):
     assert float(out[no_local.to(dev)].float().abs().max() if bool(no_local.any()) else 0.0) == 0.0
 
 
+@pytest.mark.parametrize("T", [16, 200, 1024, 1100, 2048])
+def test_every_token_on_the_same_eight_local_experts(pkg, dev, W, T):
+    """The case the workspace is sized for: a bias that makes every token select local experts 0..7, so the call has
+    8 T rows (the row capacity) on eight experts with T rows each: the largest tiles-per-expert count of every path."""
+    tok = pkg.gen.make_tokens(T, 31, dev)
+    bias = tok.routing_bias.float()
+    bias[:8] += 10.0
+    tok.routing_bias = bias.to(torch.bfloat16)
+    out = run_op(pkg, tok, W, 0)
+    ref = moe_oracle.run_full(tok.routing_logits, tok.routing_bias, tok.hidden_states, tok.hidden_states_scale,
+                              W.gemm1_weights, W.gemm1_weights_scale, W.gemm2_weights, W.gemm2_weights_scale, 0, RSF)
+    assert ref.counts[:8].tolist() == [T] * 8 and int(ref.counts.sum()) == 8 * T
+    im = assert_selection_and_permutation(pkg, T, torch.sort(ref.topk_idx.cpu(), dim=1).values, ref.counts,
+                                          ref.offsets, ref.perm_token, ref.perm_weight.cpu())
+    assert im["n_sel"] == 8 * T
+    assert_output_close(out, ref.output, ref.output_f32)
+
+
 @pytest.mark.parametrize("T,seed,offset", [(8192, 21, 0), (16384, 0, 0)])
 def test_large_batch_against_gpu_oracle(pkg, dev, W, T, seed, offset):
     """Shard calls of the size one rank of the expert-parallel layer sees (8-24 k rows): 128-token tiles,
