@@ -330,6 +330,31 @@ def test_cuda_graph_replay(pkg, dev, W, T):
             assert torch.equal(out.view(torch.int16), w.view(torch.int16)), (T, rep)
 
 
+def test_two_streams_with_their_own_workspaces(pkg, dev, W):
+    """Calls on two streams, each with its own workspace, interleaved without waiting for one another: the library
+    keeps no per-call state outside the workspace (its tensor-map cache is read-mostly and locked), so each stream
+    gets the bits of a call made alone.  (Batches above 16 tokens: the decode kernel wants the device to itself.)"""
+    op, gen = pkg.op, pkg.gen
+    cases = [(300, 3), (1100, 4), (64, 5), (40, 6)]
+    toks = [gen.make_tokens(T, seed, dev) for T, seed in cases]
+    want = [run_op(pkg, t, W, 0).clone() for t in toks]
+    torch.cuda.synchronize()
+    streams = [torch.cuda.Stream(device=dev) for _ in range(2)]
+    spaces = [op.Workspace(dev) for _ in range(2)]
+    outs = [torch.zeros_like(w) for w in want]
+    for rep in range(3):
+        for i, t in enumerate(toks):
+            k = i % 2
+            with torch.cuda.stream(streams[k]):
+                op.run(t.routing_logits, t.routing_bias, t.hidden_states, t.hidden_states_scale, W.gemm1_weights,
+                       W.gemm1_weights_scale, W.gemm2_weights, W.gemm2_weights_scale, 0, RSF, outs[i], workspace=spaces[k])
+    torch.cuda.synchronize()
+    for k in range(2):
+        assert op.kernel_status(workspace=spaces[k]) == 0
+    for o, w in zip(outs, want):
+        assert torch.equal(o.view(torch.int16), w.view(torch.int16))
+
+
 def test_workspace_too_small_is_reported(pkg, dev, W):
     tok = pkg.gen.make_tokens(8, 0, dev)
     out = torch.empty(8, 7168, dtype=torch.bfloat16, device=dev)
