@@ -127,7 +127,8 @@ def _build_plan_device(topk_idx: torch.Tensor, world: int, rank: int, group=None
         table_dev = mine.view(1, -1)
     table = table_dev.cpu()                                                   # the call's one host synchronisation
     counts = table[:, :N_SHARDS].contiguous()
-    own = counts[rank].tolist()
+    rows = table.tolist()
+    own = rows[rank][:N_SHARDS]
     bounds = [0]
     for c in own:
         bounds.append(bounds[-1] + c)
@@ -135,9 +136,9 @@ def _build_plan_device(topk_idx: torch.Tensor, world: int, rank: int, group=None
     token_lists = [send_order[bounds[s]:bounds[s + 1]] for s in range(N_SHARDS)]
     per = N_SHARDS // world
     send_counts = [sum(own[d * per:(d + 1) * per]) for d in range(world)]
-    recv_counts = [int(counts[src, rank * per:(rank + 1) * per].sum()) for src in range(world)]
+    recv_counts = [sum(rows[src][rank * per:(rank + 1) * per]) for src in range(world)]
     return DispatchPlan(token_lists, send_counts, recv_counts, counts, send_order, send_shard,
-                        [int(x) for x in table[:, N_SHARDS]], row_of)
+                        [rows[r][N_SHARDS] for r in range(world)], row_of)
 
 
 def sum_shards(plan: DispatchPlan, back: torch.Tensor, T: int) -> torch.Tensor:
@@ -342,13 +343,15 @@ def _forward_p2p(self, plan: DispatchPlan, routing_logits, routing_bias, hidden_
     dev = routing_logits.device
     n_logits = routing_logits.shape[1]
     per = N_SHARDS // world
-    counts = plan.counts                                    # [world, 8] host, identical on every rank
-    totals = counts.sum(dim=0)                              # records per shard over all sources
+    # The count table as plain integers: the arithmetic below runs between the call's host synchronisation and
+    # the launches that wait for it, where every tensor operation on a nine-element tensor costs microseconds.
+    counts = plan.counts.tolist()                            # [world][8], identical on every rank
+    totals = [sum(counts[r][s] for r in range(world)) for s in range(N_SHARDS)]   # records per shard
     # Capacity of the symmetric areas.  Every rank evaluates the SAME condition from the shared table (largest
     # receive and send count over all ranks), so either all ranks (re)allocate together -- the rendezvous is
     # collective -- or none does: no rank can fail alone in front of a barrier its peers are already waiting in.
-    need_recv = max(int(totals[d * per:(d + 1) * per].sum()) for d in range(world))
-    need_send = max(int(counts[r].sum()) for r in range(world))
+    need_recv = max(sum(totals[d * per:(d + 1) * per]) for d in range(world))
+    need_send = max(sum(counts[r]) for r in range(world))
     if self._px is None or need_recv > self._px.max_recv_rows or need_send > self._px.max_send_rows:
         t_max = max(plan.tokens_per_rank)
         cap_recv = max(1, need_recv, t_max * world * per if self._px is None else 2 * need_recv)
@@ -356,13 +359,13 @@ def _forward_p2p(self, plan: DispatchPlan, routing_logits, routing_bias, hidden_
         self._px = None                                     # release the old areas first
         self._px = PeerExchange(rank, world, self.group, dev, cap_recv, cap_send, n_logits)
     px = self._px
-    n_send = int(counts[rank].sum())
-    n_recv = int(sum(int(totals[s]) for s in self.shards))
+    n_send = sum(counts[rank])
+    n_recv = sum(totals[s] for s in self.shards)
 
     def recv_row_base(d: int, s: int, src: int) -> int:
         """First row, in rank d's receive area, of the records that `src` sends for shard s (shard-major)."""
         first = d * per
-        return int(totals[first:s].sum()) + int(counts[:src, s].sum())
+        return sum(totals[first:s]) + sum(counts[r][s] for r in range(src))
 
     # No barrier is needed before the push.  The receive areas it overwrites were last read by the owners' shard
     # operators of the previous call, and every rank passed that call's exit barrier only after its own shard
@@ -372,7 +375,7 @@ def _forward_p2p(self, plan: DispatchPlan, routing_logits, routing_bias, hidden_
     by_shard = (loader.EpSegment * N_SHARDS)()               # the same, indexed by shard (count 0: none)
     nseg, first = 0, 0
     for s in range(N_SHARDS):
-        n = int(counts[rank, s])
+        n = counts[rank][s]
         if n:
             d = owner_of_shard(s, world)
             row = recv_row_base(d, s, rank)
@@ -402,8 +405,8 @@ def _forward_p2p(self, plan: DispatchPlan, routing_logits, routing_bias, hidden_
         seg_base, seg_cnt = [], []
         for s in self.shards:
             for src in range(world):
-                seg_base.append(px.ptrs[src] + px.off_back + int(counts[src, :s].sum()) * H * 2)
-                seg_cnt.append(int(counts[src, s]))
+                seg_base.append(px.ptrs[src] + px.off_back + sum(counts[src][:s]) * H * 2)
+                seg_cnt.append(counts[src][s])
         nseg = len(seg_base)
         base_arr = (ctypes.c_int64 * nseg)(*seg_base)
         cnt_arr = (ctypes.c_int64 * nseg)(*seg_cnt)
@@ -417,7 +420,7 @@ def _forward_p2p(self, plan: DispatchPlan, routing_logits, routing_bias, hidden_
     row0 = 0
     self.last_shard_rows = []
     for j, s in enumerate(self.shards):
-        n_s = int(totals[s])
+        n_s = totals[s]
         self.last_shard_rows.append(n_s)
         if n_s:
             rows = slice(row0, row0 + n_s)
