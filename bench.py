@@ -114,10 +114,12 @@ class ClockSampler:
     FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
               "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
 
-    def __init__(self, index: int):
-        self.index, self.lines, self.proc, self.first = index, [], None, 0
+    def __init__(self, index: int, enabled: bool = True):
+        self.index, self.lines, self.proc, self.first, self.enabled = index, [], None, 0, enabled
 
     def __enter__(self):
+        if not self.enabled:      # multi-rank runs: one poller (rank 0's) is enough, eight perturb the launches
+            return self
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "20",
@@ -619,7 +621,8 @@ def bench_ep(args):
         sync()
         l0 = loader.launch_count()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        with ClockSampler(local_rank) as cs:
+        with ClockSampler(local_rank, enabled=(rank == 0 and clocks is None)) as cs:
+            sync()      # rank 0 waited for its sampler's first line: the ranks start the timed steps together
             e0.record()
             for _ in range(args.steps):
                 out = step()
