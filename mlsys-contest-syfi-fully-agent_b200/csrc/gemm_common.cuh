@@ -116,8 +116,6 @@ __device__ __forceinline__ bool grid_barrier_wait(unsigned int* word2, unsigned 
   }
 }
 
-// K-blocks per pipeline stage of the decode kernel.
-constexpr int kDecodeKps = 2;
 // Up to this many tokens the decode kernel routes with one thread per expert (see decode_route_schedule).
 constexpr int kBlockRouteMaxTokens = 4;
 

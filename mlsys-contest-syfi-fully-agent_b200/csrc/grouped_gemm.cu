@@ -468,19 +468,17 @@ int init_one() {
 int grouped_gemm_kblocks_per_stage(int gemm_id, int n_tile) {
 #define MOE_CASE(G, N) \
   if (gemm_id == G && n_tile == N) return Cfg<G, N>::KPS;
-  MOE_CASE(1, 16) MOE_CASE(1, 32) MOE_CASE(1, 64) MOE_CASE(1, 128)
-  MOE_CASE(2, 16) MOE_CASE(2, 32) MOE_CASE(2, 64) MOE_CASE(2, 128)
+  MOE_CASE(1, 32) MOE_CASE(1, 64) MOE_CASE(1, 128)
+  MOE_CASE(2, 32) MOE_CASE(2, 64) MOE_CASE(2, 128)
 #undef MOE_CASE
   return 1;
 }
 
 int grouped_gemm_init() {
   int rc = 0;
-  if ((rc = init_one<1, 16>())) return rc;
   if ((rc = init_one<1, 32>())) return rc;
   if ((rc = init_one<1, 64>())) return rc;
   if ((rc = init_one<1, 128>())) return rc;
-  if ((rc = init_one<2, 16>())) return rc;
   if ((rc = init_one<2, 32>())) return rc;
   if ((rc = init_one<2, 64>())) return rc;
   if ((rc = init_one<2, 128>())) return rc;
@@ -493,8 +491,8 @@ int launch_grouped_gemm(int gemm_id, int n_tile, const CUtensorMap& tm_w, const 
                         int ctas, cudaStream_t stream) {
 #define MOE_CASE(G, N) \
   if (gemm_id == G && n_tile == N) return launch_one<G, N>(tm_w, tm_b, a, ctas, stream);
-  MOE_CASE(1, 16) MOE_CASE(1, 32) MOE_CASE(1, 64) MOE_CASE(1, 128)
-  MOE_CASE(2, 16) MOE_CASE(2, 32) MOE_CASE(2, 64) MOE_CASE(2, 128)
+  MOE_CASE(1, 32) MOE_CASE(1, 64) MOE_CASE(1, 128)
+  MOE_CASE(2, 32) MOE_CASE(2, 64) MOE_CASE(2, 128)
 #undef MOE_CASE
   return static_cast<int>(cudaErrorInvalidValue);
 }

@@ -140,6 +140,7 @@ int grouped_gemm_row_step(int n_tile);   // rows per step: n_tile / 4 from 64-to
 int launch_grouped_gemm(int gemm_id, int n_tile, const CUtensorMap& tm_w, const TokenMaps& tm_b, const GemmArgs& a,
                         int ctas, cudaStream_t stream);
 constexpr int kFusedMaxTokens = 16;
+constexpr int kDecodeKps = 2;   // K-blocks per pipeline stage (and per TMA box) of the decode kernel
 // Decode path in one launch: routing, GEMM1, SwiGLU, GEMM2 and combine (decode_kernel.cu).  `g` is the GEMM1 view
 // of the arguments with all routing / tail fields set; tm_x maps hidden_states, tm_c the SwiGLU planes.
 int launch_decode(const CUtensorMap& tm_w1, const CUtensorMap& tm_x, const CUtensorMap& tm_w2, const CUtensorMap& tm_c,

@@ -302,7 +302,9 @@ static int run_impl(const float* routing_logits, const uint16_t* routing_bias, c
   const int ctas = dev->sm_count;
 
   CUtensorMap tm_w13, tm_w2, tm_a, tm_c;
-  const uint32_t kps1 = grouped_gemm_kblocks_per_stage(1, n_tile), kps2 = grouped_gemm_kblocks_per_stage(2, n_tile2);
+  const bool decode = T <= kFusedMaxTokens;
+  const uint32_t kps1 = decode ? kDecodeKps : grouped_gemm_kblocks_per_stage(1, n_tile);
+  const uint32_t kps2 = decode ? kDecodeKps : grouped_gemm_kblocks_per_stage(2, n_tile2);
   // (the large-batch kernels take one K-block per box)
   if ((rc = get_map(dev, kblock_map(gemm1_weights, static_cast<uint64_t>(kELocal) * k2I, kH, 128, large ? 1 : kps1), &tm_w13)))
     return rc;
